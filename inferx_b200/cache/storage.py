@@ -1,7 +1,7 @@
 """Device memory behind the cache manager's bookkeeping.
 
 Per layer with a paged need: one tensor ``[pages, kv_heads, page_size, head_dim]``
-for each entry of the need (keys and values for attention; whatever a mixer names),
+(or the entry's own head size, where the need gives one) for each entry of the need (keys and values for attention; whatever a mixer names),
 indexed by the page ids of the layer's group (the reference's per-layer views are
 ``[P, B, kv_heads, hd]``, include/inferx/core/kv_cache.h:40-150; heads are moved
 outward here so that one head's part of a page is contiguous).  Per state need of a
@@ -34,11 +34,13 @@ class CacheStorage:
                         raise TypeError(f"layer {layer}: paged needs with different windows; "
                                         "one block table addresses a layer's pages")
                     pages = manager.pools[g].num_pages
-                    shape = (pages, need.kv_heads, manager.page_size, need.head_dim)
+                    dims = getattr(need, "entry_dims", None)
                     per = self.paged.setdefault(layer, {})
-                    for name in getattr(need, "entries", ("k", "v")):
+                    for i, name in enumerate(getattr(need, "entries", ("k", "v"))):
                         if name in per:
                             raise TypeError(f"layer {layer}: paged entry {name!r} named twice")
+                        shape = (pages, need.kv_heads, manager.page_size,
+                                 need.head_dim if dims is None else int(dims[i]))
                         per[name] = torch.zeros(shape, dtype=getattr(need, "dtype", None) or dtype,
                                                 device=self.device)
                 elif isinstance(need, StateNeed) or hasattr(need, "shape"):

@@ -64,6 +64,10 @@ def _register_builtin():
     from .tinapel_config import TinapelConfig
     register_architecture(TinapelConfig.ARCHITECTURE, TinapelConfig.from_json,
                           tinapel.build_spec, replace=True)
+    from ..models import mapovik
+    from .mapovik_config import MapovikConfig
+    register_architecture(MapovikConfig.ARCHITECTURE, MapovikConfig.from_json,
+                          mapovik.build_spec, replace=True)
 
 
 _register_builtin()

@@ -1,6 +1,7 @@
 // Paged causal attention with grouped KV heads and an optional sliding window,
 // for any mix of prompt portions and single decoded tokens in one launch.
-// This is the general kernel: any head size up to 512, any element type, fp32
+// This is the general kernel: any head size up to 512 (the values' may differ from the
+// keys'), any element type, fp32
 // arithmetic throughout with the accurate expf.  It is the whole attention of
 // the 32-bit path and the fallback of the bfloat16 path for shapes the tuned
 // kernels refuse.
@@ -25,8 +26,8 @@ paged_attention_generic_kernel(const TA* __restrict__ q, const TA* __restrict__ 
                                const TA* __restrict__ vc, const int* __restrict__ block_table,
                                const int* __restrict__ seq_of_token,
                                const int* __restrict__ positions, TA* __restrict__ out, int heads,
-                               int kvh, int hd, int page_size, int max_blocks, int window,
-                               float scale, float softcap) {
+                               int kvh, int hd, int vd, int page_size, int max_blocks,
+                               int window, float scale, float softcap) {
   extern __shared__ float smem[];
   float* qs = smem;        // [hd]
   float* sc = smem + hd;   // [ATT_TILE]
@@ -83,22 +84,22 @@ paged_attention_generic_kernel(const TA* __restrict__ q, const TA* __restrict__ 
       const int kp = tile0 + j;
       const int page = bt[kp / page_size];
       const int off = kp % page_size;
-      const TA* vrow = vc + (((size_t)page * kvh + kh) * page_size + off) * hd;
+      const TA* vrow = vc + (((size_t)page * kvh + kh) * page_size + off) * vd;
       const float p = sc[j];
 #pragma unroll
       for (int i = 0; i < ATT_MAX_DPT; ++i) {
         const int d = threadIdx.x + i * ATT_THREADS;
-        if (d < hd) acc[i] += p * to_f32(vrow[d]);
+        if (d < vd) acc[i] += p * to_f32(vrow[d]);
       }
     }
     __syncthreads();
   }
-  TA* orow = out + ((size_t)t * heads + h) * hd;
+  TA* orow = out + ((size_t)t * heads + h) * vd;
   const float inv_l = 1.0f / l;
 #pragma unroll
   for (int i = 0; i < ATT_MAX_DPT; ++i) {
     const int d = threadIdx.x + i * ATT_THREADS;
-    if (d < hd) orow[d] = from_f32<TA>(acc[i] * inv_l);
+    if (d < vd) orow[d] = from_f32<TA>(acc[i] * inv_l);
   }
 }
 
@@ -109,12 +110,14 @@ IX_API int ix_attention_max_head_dim() { return ATT_THREADS * ATT_MAX_DPT; }
 IX_API int ix_paged_attention_generic(const void* q, const void* k_cache, const void* v_cache,
                                       const int* block_table, const int* seq_of_token,
                                       const int* positions, void* out, int act_dtype, int T,
-                                      int heads, int kvh, int hd, int page_size, int max_blocks,
-                                      int window, float scale, float softcap, cudaStream_t stream) {
+                                      int heads, int kvh, int hd, int vd, int page_size,
+                                      int max_blocks, int window, float scale, float softcap,
+                                      cudaStream_t stream) {
   if (T <= 0) return IX_OK;
   if (heads <= 0 || kvh <= 0 || heads % kvh != 0 || page_size <= 0 || max_blocks <= 0)
     return IX_ERR_SIZE;
   if (hd <= 0 || hd > ATT_THREADS * ATT_MAX_DPT) return IX_ERR_SIZE;
+  if (vd <= 0 || vd > ATT_THREADS * ATT_MAX_DPT) return IX_ERR_SIZE;   // values of another size
   if (window < 0) return IX_ERR_SIZE;
   const size_t smem = (size_t)(hd + ATT_TILE) * sizeof(float);
   if (heads > 65535) return IX_ERR_SIZE;
@@ -122,7 +125,7 @@ IX_API int ix_paged_attention_generic(const void* q, const void* k_cache, const 
   IX_DISPATCH_DTYPE(act_dtype, TA,
                     (paged_attention_generic_kernel<TA><<<grid, ATT_THREADS, smem, stream>>>(
                         (const TA*)q, (const TA*)k_cache, (const TA*)v_cache, block_table,
-                        seq_of_token, positions, (TA*)out, heads, kvh, hd, page_size, max_blocks,
-                        window, scale, softcap)));
+                        seq_of_token, positions, (TA*)out, heads, kvh, hd, vd, page_size,
+                        max_blocks, window, scale, softcap)));
   return ix_launch_status();
 }

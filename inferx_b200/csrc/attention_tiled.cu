@@ -49,15 +49,16 @@ __global__ void __launch_bounds__(TA_THREADS)
 paged_attention_tiled_kernel(const TA* __restrict__ q, const TA* __restrict__ kc,
                              const TA* __restrict__ vc, const int* __restrict__ block_table,
                              const int* __restrict__ cu_q, const int* __restrict__ q_pos0,
-                             TA* __restrict__ out, int S, int heads, int kvh, int hd,
+                             TA* __restrict__ out, int S, int heads, int kvh, int hd, int vd,
                              int page_size, int max_blocks, int window, float scale,
                              float softcap) {
   extern __shared__ __align__(16) float tsm[];
   const int ld = hd + 4;                         // row pitch: 16-byte rows, no bank conflicts
+  const int ldv = vd + 4;                        // the values' size may differ from the keys'
   float* Qs = tsm;                               // [TA_BQ][ld]
   float* Ks = Qs + TA_BQ * ld;                   // [TA_BK][ld]
-  float* Vs = Ks + TA_BK * ld;                   // [TA_BK][ld]
-  float* Ps = Vs + TA_BK * ld;                   // [TA_BQ][TA_BK + 4]
+  float* Vs = Ks + TA_BK * ld;                   // [TA_BK][ldv]
+  float* Ps = Vs + TA_BK * ldv;                  // [TA_BQ][TA_BK + 4]
   float* m_run = Ps + TA_BQ * (TA_BK + 4);       // [TA_BQ]
   float* l_run = m_run + TA_BQ;
   float* corr = l_run + TA_BQ;
@@ -80,6 +81,7 @@ paged_attention_tiled_kernel(const TA* __restrict__ q, const TA* __restrict__ kc
   const int* bt = block_table + (size_t)s * max_blocks;
   const int tid = threadIdx.x;
   const int chunks = hd >> 2;
+  const int vchunks = vd >> 2;
 
   for (int idx = tid; idx < TA_BQ * chunks; idx += TA_THREADS) {
     const int r = idx / chunks, c = idx - r * chunks;
@@ -109,17 +111,28 @@ paged_attention_tiled_kernel(const TA* __restrict__ q, const TA* __restrict__ kc
     for (int idx = tid; idx < TA_BK * chunks; idx += TA_THREADS) {
       const int r = idx / chunks, c = idx - r * chunks;
       const int kp = kv0 + r;
-      float4 kv4 = make_float4(0.f, 0.f, 0.f, 0.f), vv4 = kv4;
+      float4 kv4 = make_float4(0.f, 0.f, 0.f, 0.f);
       if (kp >= kv_lo && kp < kv_hi) {
         const int page = bt[kp / page_size];
         if (page >= 0) {
           const size_t row = (((size_t)page * kvh + kh) * page_size + kp % page_size) * hd;
           kv4 = TaLoad4<TA>::load(kc + row + 4 * c);
-          vv4 = TaLoad4<TA>::load(vc + row + 4 * c);
         }
       }
       *reinterpret_cast<float4*>(Ks + r * ld + 4 * c) = kv4;
-      *reinterpret_cast<float4*>(Vs + r * ld + 4 * c) = vv4;
+    }
+    for (int idx = tid; idx < TA_BK * vchunks; idx += TA_THREADS) {
+      const int r = idx / vchunks, c = idx - r * vchunks;
+      const int kp = kv0 + r;
+      float4 vv4 = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (kp >= kv_lo && kp < kv_hi) {
+        const int page = bt[kp / page_size];
+        if (page >= 0) {
+          const size_t row = (((size_t)page * kvh + kh) * page_size + kp % page_size) * vd;
+          vv4 = TaLoad4<TA>::load(vc + row + 4 * c);
+        }
+      }
+      *reinterpret_cast<float4*>(Vs + r * ldv + 4 * c) = vv4;
     }
     __syncthreads();
 
@@ -201,8 +214,8 @@ paged_attention_tiled_kernel(const TA* __restrict__ q, const TA* __restrict__ kc
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         const int d = 4 * ol + 128 * j;
-        if (d < hd) {
-          const float4 v4 = *reinterpret_cast<const float4*>(Vs + k * ld + d);
+        if (d < vd) {
+          const float4 v4 = *reinterpret_cast<const float4*>(Vs + k * ldv + d);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             acc[i][j][0] = fmaf(p[i], v4.x, acc[i][j][0]);
@@ -223,8 +236,8 @@ paged_attention_tiled_kernel(const TA* __restrict__ q, const TA* __restrict__ kc
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
       const int d = 4 * ol + 128 * j;
-      if (d < hd)
-        TaLoad4<TA>::store(out + ((size_t)(tok0 + r) * heads + h) * hd + d,
+      if (d < vd)
+        TaLoad4<TA>::store(out + ((size_t)(tok0 + r) * heads + h) * vd + d,
                            make_float4(acc[i][j][0] * inv_l, acc[i][j][1] * inv_l,
                                        acc[i][j][2] * inv_l, acc[i][j][3] * inv_l));
     }
@@ -233,24 +246,27 @@ paged_attention_tiled_kernel(const TA* __restrict__ q, const TA* __restrict__ kc
 
 IX_API int ix_paged_attention_tiled_applies(int hd) { return hd > 0 && hd % 4 == 0 && hd <= 256; }
 
-// q, out: [T, heads, hd]; caches [pages, kvh, page_size, hd]; block_table [S, max_blocks];
+// q: [T, heads, hd]; out: [T, heads, vd]; caches [pages, kvh, page_size, hd or vd];
+// block_table [S, max_blocks];
 // cu_q [S + 1]: token range of each sequence; q_pos0 [S]: position of its first token here.
 IX_API int ix_paged_attention_tiled(const void* q, const void* k_cache, const void* v_cache,
                                     const int* block_table, const int* cu_q, const int* q_pos0,
                                     void* out, int act_dtype, int T, int S, int heads, int kvh,
-                                    int hd, int page_size, int max_blocks, int window,
+                                    int hd, int vd, int page_size, int max_blocks, int window,
                                     float scale, float softcap, cudaStream_t stream) {
   if (T <= 0) return IX_OK;
   if (S <= 0 || heads <= 0 || kvh <= 0 || heads % kvh != 0 || page_size <= 0 || max_blocks <= 0 ||
       window < 0)
     return IX_ERR_SIZE;
-  if (!ix_paged_attention_tiled_applies(hd)) return IX_ERR_UNSUPPORTED;
+  if (!ix_paged_attention_tiled_applies(hd) || !ix_paged_attention_tiled_applies(vd))
+    return IX_ERR_UNSUPPORTED;
   if ((T + TA_BQ - 1) / TA_BQ + S > 65535) return IX_ERR_SIZE;
   const int esize = act_dtype == IX_F32 ? 4 : 2;
   if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) % (4 * esize))
     return IX_ERR_ALIGN;
-  const int ld = hd + 4;
-  const size_t smem = ((size_t)(TA_BQ + 2 * TA_BK) * ld + TA_BQ * (TA_BK + 4) + 3 * TA_BQ) * 4;
+  const int ld = hd + 4, ldv = vd + 4;
+  const size_t smem = ((size_t)(TA_BQ + TA_BK) * ld + (size_t)TA_BK * ldv + TA_BQ * (TA_BK + 4) +
+                       3 * TA_BQ) * 4;
   dim3 grid(heads, (T + TA_BQ - 1) / TA_BQ + S);   // every sequence can add a partial tile
   IX_DISPATCH_DTYPE(act_dtype, TA, {
     auto kern = paged_attention_tiled_kernel<TA>;
@@ -261,7 +277,7 @@ IX_API int ix_paged_attention_tiled(const void* q, const void* k_cache, const vo
     }
     kern<<<grid, TA_THREADS, smem, stream>>>((const TA*)q, (const TA*)k_cache, (const TA*)v_cache,
                                              block_table, cu_q, q_pos0, (TA*)out, S, heads, kvh,
-                                             hd, page_size, max_blocks, window, scale,
+                                             hd, vd, page_size, max_blocks, window, scale,
                                              softcap);
   });
   return ix_launch_status();

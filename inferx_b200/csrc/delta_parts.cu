@@ -1,0 +1,636 @@
+// Kernels of layers built around a short causal convolution and a recurrence with a
+// matrix of state per head and request, and of the pre-norm arrangement with a scaled
+// residual and a centred norm:
+//
+//   add + norm          resid += scale * delta (+ vector); out = norm(resid) * gain, where
+//                       norm subtracts the mean (layer norm) or not (RMS norm)
+//   stream concat       out[t] = [resid[t] + scale * delta[t] ; first[t]] in the run's type
+//   causal convolution  y[t][c] = act(b[c] + sum_j w[c][j] x[t - (taps-1) + j][c]) with the
+//                       taps-1 inputs before a sequence's first token of the step taken
+//                       from per-request state, which a second kernel then moves on
+//   state space         S = exp(-exp(A) dt) S + dt B x^T;  y = S^T C + D x   (scalar decay)
+//   gated delta rule    S = diag(g) S;  u = beta (v - S^T k);  S += k u^T;  o = S^T q
+//   gate + group norm   out = groupnorm(y * silu(z)) * gain
+//   normed pair mean    out = (l / rms(l) * gl + r / rms(r) * gr) / 2
+//   relu squared, table routing, scaling of rows
+//
+// Everything but the stored activations is fp32 with the accurate library functions.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------
+// add + norm.  One block per output row; the row is kept in shared memory between the
+// passes (mean, then the mean of squared deviations, then the output).
+// ---------------------------------------------------------------------------
+template <typename TD, typename TO>
+__global__ void add_scaled_norm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
+                                       float scale, const float* __restrict__ vector,
+                                       const float* __restrict__ gain,
+                                       const int* __restrict__ rows, TO* __restrict__ out, int H,
+                                       float eps, int center, int write_back) {
+  extern __shared__ __align__(16) float row_s[];   // [H] + 32
+  float* scratch = row_s + H;
+  IX_PDL_WAIT();
+  const int r = blockIdx.x;
+  const size_t src = rows ? (size_t)rows[r] : (size_t)r;
+  float* x = resid + src * H;
+  float sum = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = x[i];
+    if (delta) v += scale * to_f32(delta[src * H + i]);
+    if (vector) v += vector[i];
+    row_s[i] = v;
+    if (write_back) x[i] = v;
+    sum += v;
+  }
+  float mean = 0.f;
+  if (center) mean = block_sum(sum, scratch) / (float)H;
+  else __syncthreads();
+  float sq = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float d = row_s[i] - mean;
+    sq += d * d;
+  }
+  const float inv = 1.0f / sqrtf(block_sum(sq, scratch) / (float)H + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x)
+    out[(size_t)r * H + i] = from_f32<TO>((row_s[i] - mean) * inv * gain[i]);
+}
+
+IX_API int ix_add_scaled_norm(float* resid, const void* delta, int delta_dtype, float scale,
+                              const float* vector, const float* gain, const int* rows, void* out,
+                              int out_dtype, int R, int H, float eps, int center, int write_back,
+                              cudaStream_t stream) {
+  if (R <= 0) return IX_OK;
+  if (H <= 0) return IX_ERR_SIZE;
+  const size_t smem = (size_t)(H + 32) * sizeof(float);
+  if (smem > 200 * 1024) return IX_ERR_SMEM;
+  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+#define IX_ASN(TD, TO)                                                                       \
+  do {                                                                                       \
+    auto kern = add_scaled_norm_kernel<TD, TO>;                                              \
+    if (smem > 48 * 1024)                                                                    \
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
+    ix_launch(kern, dim3(R), dim3(threads), smem, stream, resid, (const TD*)delta, scale,    \
+              vector, gain, rows, (TO*)out, H, eps, center, write_back);                     \
+  } while (0)
+  if (out_dtype == IX_F32) {
+    if (delta_dtype == IX_F32) IX_ASN(float, float);
+    else if (delta_dtype == IX_BF16) IX_ASN(bf16, float);
+    else return IX_ERR_DTYPE;
+  } else if (out_dtype == IX_BF16) {
+    if (delta_dtype == IX_F32) IX_ASN(float, bf16);
+    else if (delta_dtype == IX_BF16) IX_ASN(bf16, bf16);
+    else return IX_ERR_DTYPE;
+  } else {
+    return IX_ERR_DTYPE;
+  }
+#undef IX_ASN
+  return ix_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// stream concat: out[t] = [resid[t] + scale * delta[t] (+ vector) ; first[t]].
+// ---------------------------------------------------------------------------
+template <typename TD, typename TO>
+__global__ void stream_concat_kernel(const float* __restrict__ resid,
+                                     const TD* __restrict__ delta, float scale,
+                                     const float* __restrict__ vector,
+                                     const float* __restrict__ first, TO* __restrict__ out, int T,
+                                     int H) {
+  IX_PDL_WAIT();
+  const size_t n = (size_t)T * H;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / H, c = i - t * H;
+    float v = resid[i];
+    if (delta) v += scale * to_f32(delta[i]);
+    if (vector) v += vector[c];
+    out[t * 2 * H + c] = from_f32<TO>(v);
+    out[t * 2 * H + H + c] = from_f32<TO>(first[i]);
+  }
+}
+
+IX_API int ix_stream_concat(const float* resid, const void* delta, int delta_dtype, float scale,
+                            const float* vector, const float* first, void* out, int out_dtype,
+                            int T, int H, cudaStream_t stream) {
+  if (T <= 0) return IX_OK;
+  if (H <= 0) return IX_ERR_SIZE;
+  const size_t n = (size_t)T * H;
+  const int blocks = (int)((n + 255) / 256 > 148 * 16 ? 148 * 16 : (n + 255) / 256);
+#define IX_SC(TD, TO)                                                                      \
+  ix_launch(stream_concat_kernel<TD, TO>, dim3(blocks), dim3(256), 0, stream, resid,      \
+            (const TD*)delta, scale, vector, first, (TO*)out, T, H)
+  if (out_dtype == IX_F32) {
+    if (delta_dtype == IX_F32) IX_SC(float, float);
+    else IX_SC(bf16, float);
+  } else if (out_dtype == IX_BF16) {
+    if (delta_dtype == IX_F32) IX_SC(float, bf16);
+    else IX_SC(bf16, bf16);
+  } else {
+    return IX_ERR_DTYPE;
+  }
+#undef IX_SC
+  return ix_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// causal convolution over time per channel.  x [T, C] is a view with row pitch ldx;
+// w [C, taps] (the last column multiplies the current token); state [slots, taps-1, C]
+// holds a request's last taps-1 inputs (oldest first).  A thread owns one channel of one
+// token; the sum runs from the oldest tap to the newest whatever the step's cut.
+// ---------------------------------------------------------------------------
+#define CONV_THREADS 128
+#define CONV_MAX_TAPS 16
+
+template <typename TA>
+__global__ void causal_conv_kernel(const TA* __restrict__ x, long long ldx,
+                                   const float* __restrict__ w, const float* __restrict__ bias,
+                                   const float* __restrict__ state,
+                                   const int* __restrict__ cu_q,
+                                   const int* __restrict__ seq_of_token,
+                                   const int* __restrict__ state_slot, TA* __restrict__ out,
+                                   int C, int taps, int act) {
+  IX_PDL_WAIT();
+  const int t = blockIdx.x;
+  const int c = blockIdx.y * CONV_THREADS + threadIdx.x;
+  if (c >= C) return;
+  const int s = seq_of_token[t];
+  const int begin = cu_q[s];
+  const float* st = state + (size_t)state_slot[s] * (taps - 1) * C;
+  float acc = bias ? bias[c] : 0.f;
+  for (int j = 0; j < taps; ++j) {
+    const int src = t - (taps - 1) + j;          // token index of this tap's input
+    float v;
+    if (src >= begin) {
+      v = to_f32(x[(size_t)src * ldx + c]);
+    } else {
+      // begin - src inputs back from the step's first token: 1 is the newest kept one
+      const int back = begin - src;               // 1 .. taps-1
+      v = st[(size_t)(taps - 1 - back) * C + c];
+    }
+    acc = fmaf(w[(size_t)c * taps + j], v, acc);
+  }
+  if (act) acc = acc / (1.0f + expf(-acc));
+  out[(size_t)t * C + c] = from_f32<TA>(acc);
+}
+
+// The state moves on: entry i becomes the input taps-1-i tokens before the sequence's
+// next token.  A thread owns one channel of one sequence and walks i upwards; what it
+// reads from the old state lies above what it has written.
+template <typename TA>
+__global__ void conv_state_update_kernel(const TA* __restrict__ x, long long ldx,
+                                         float* __restrict__ state, const int* __restrict__ cu_q,
+                                         const int* __restrict__ state_slot, int C, int taps) {
+  IX_PDL_WAIT();
+  const int s = blockIdx.x;
+  const int c = blockIdx.y * CONV_THREADS + threadIdx.x;
+  if (c >= C) return;
+  const int begin = cu_q[s], n = cu_q[s + 1] - begin;
+  if (n <= 0) return;
+  float* st = state + (size_t)state_slot[s] * (taps - 1) * C;
+  for (int i = 0; i < taps - 1; ++i) {
+    const int src = n - (taps - 1) + i;           // index among this step's tokens
+    const float v = src >= 0 ? to_f32(x[(size_t)(begin + src) * ldx + c])
+                             : st[(size_t)(i + n) * C + c];
+    st[(size_t)i * C + c] = v;
+  }
+}
+
+IX_API int ix_causal_conv(const void* x, int dtype, long long ldx, const float* w,
+                          const float* bias, float* state, const int* cu_q,
+                          const int* seq_of_token, const int* state_slot, void* out, int T, int S,
+                          int C, int taps, int act, cudaStream_t stream) {
+  if (T <= 0 || S <= 0) return IX_OK;
+  if (C <= 0 || taps < 1 || taps > CONV_MAX_TAPS || ldx < C) return IX_ERR_SIZE;
+  const int cb = (C + CONV_THREADS - 1) / CONV_THREADS;
+  if (cb > 65535) return IX_ERR_SIZE;
+  IX_DISPATCH_DTYPE(dtype, TA, {
+    ix_launch(causal_conv_kernel<TA>, dim3(T, cb), dim3(CONV_THREADS), 0, stream, (const TA*)x,
+              ldx, w, bias, (const float*)state, cu_q, seq_of_token, state_slot, (TA*)out, C,
+              taps, act);
+    if (taps > 1)
+      ix_launch(conv_state_update_kernel<TA>, dim3(S, cb), dim3(CONV_THREADS), 0, stream,
+                (const TA*)x, ldx, state, cu_q, state_slot, C, taps);
+  });
+  return ix_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// The two recurrences.  grid (ceil(V / 32), heads, sequences); a block is 32 value columns
+// times KS slices of the key (state) channels, one warp a slice.  A thread keeps its KPT
+// entries of one state column in registers while it walks the sequence's tokens of the
+// step in chunks of RC_CHUNK staged in shared memory.  A token's arithmetic depends on the
+// token and the state alone, and every sum has an order fixed by (K, KS): a position's
+// output does not depend on how its sequence was cut into steps or on the batch.
+// ---------------------------------------------------------------------------
+#define RC_COLS 32
+#define RC_CHUNK 16
+
+__device__ __forceinline__ float softplus_f(float z) {
+  return z > 20.f ? z : log1pf(expf(z));
+}
+
+// state space: q = C, k = dt * B, scalar decay a = exp(-exp(A) dt), skip D x.  Slices do
+// not interact inside a token, so they meet once per chunk.
+template <typename TA, int KPT>
+__global__ void __launch_bounds__(RC_COLS * 8)
+ssd_recurrence_kernel(const TA* __restrict__ xbc, long long ld, const TA* __restrict__ dt_raw,
+                      long long ld_dt, const float* __restrict__ dt_bias,
+                      const float* __restrict__ a_log, const float* __restrict__ d_skip,
+                      float* __restrict__ state, const int* __restrict__ cu_q,
+                      const int* __restrict__ state_slot, float* __restrict__ out, int H, int V,
+                      int K, int G, int KS) {
+  extern __shared__ __align__(16) float sm[];
+  float* c_s = sm;                          // [RC_CHUNK][K]   C_t
+  float* k_s = c_s + RC_CHUNK * K;          // [RC_CHUNK][K]   dt * B_t
+  float* v_s = k_s + RC_CHUNK * K;          // [RC_CHUNK][RC_COLS]  x_t
+  float* a_s = v_s + RC_CHUNK * RC_COLS;    // [RC_CHUNK]
+  float* part = a_s + RC_CHUNK;             // [KS][RC_CHUNK][RC_COLS]
+  IX_PDL_WAIT();
+  const int lane = threadIdx.x & 31, ks = threadIdx.x >> 5;
+  const int v0 = blockIdx.x * RC_COLS, h = blockIdx.y, s = blockIdx.z;
+  const int col = v0 + lane;
+  const bool col_ok = col < V;
+  const int g = h / (H / G);
+  const int inner = H * V;
+  const int t_begin = cu_q[s], t_end = cu_q[s + 1];
+  if (t_end <= t_begin) return;
+  float* st = state + ((size_t)state_slot[s] * H + h) * K * V;
+  const int kk0 = ks * KPT;
+  const float neg_a = -expf(a_log[h]), bias = dt_bias[h], dsk = d_skip[h];
+  float S[KPT];
+#pragma unroll
+  for (int i = 0; i < KPT; ++i) {
+    const int kk = kk0 + i;
+    S[i] = (kk < K && col_ok) ? st[(size_t)kk * V + col] : 0.f;
+  }
+  for (int t0 = t_begin; t0 < t_end; t0 += RC_CHUNK) {
+    const int n = min(RC_CHUNK, t_end - t0);
+    if (threadIdx.x < n) {
+      const float dt = softplus_f(to_f32(dt_raw[(size_t)(t0 + threadIdx.x) * ld_dt + h]) + bias);
+      a_s[threadIdx.x] = expf(neg_a * dt);
+      part[threadIdx.x] = dt;               // borrowed until the next barrier
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n * K; i += blockDim.x) {
+      const int c = i / K, kk = i - c * K;
+      const TA* row = xbc + (size_t)(t0 + c) * ld + inner + (size_t)g * K + kk;
+      k_s[i] = __fmul_rn(part[c], to_f32(row[0]));
+      c_s[i] = to_f32(row[(size_t)G * K]);
+    }
+    for (int i = threadIdx.x; i < n * RC_COLS; i += blockDim.x) {
+      const int c = i / RC_COLS, j = i - c * RC_COLS;
+      v_s[i] = (v0 + j < V) ? to_f32(xbc[(size_t)(t0 + c) * ld + (size_t)h * V + v0 + j]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll 2
+    for (int c = 0; c < n; ++c) {
+      const float vj = v_s[c * RC_COLS + lane], a = a_s[c];
+      const float* kc = k_s + c * K + kk0;
+      const float* cc = c_s + c * K + kk0;
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < KPT; ++i) {
+        if (kk0 + i < K) {
+          S[i] = __fmaf_rn(a, S[i], __fmul_rn(kc[i], vj));
+          acc = __fmaf_rn(S[i], cc[i], acc);
+        }
+      }
+      part[(ks * RC_CHUNK + c) * RC_COLS + lane] = acc;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n * RC_COLS; i += blockDim.x) {
+      const int c = i / RC_COLS, j = i - c * RC_COLS;
+      if (v0 + j < V) {
+        float total = 0.f;
+        for (int w = 0; w < KS; ++w) total += part[(w * RC_CHUNK + c) * RC_COLS + j];
+        out[((size_t)(t0 + c) * H + h) * V + v0 + j] = __fmaf_rn(dsk, v_s[i], total);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < KPT; ++i) {
+    const int kk = kk0 + i;
+    if (kk < K && col_ok) st[(size_t)kk * V + col] = S[i];
+  }
+}
+
+// gated delta rule.  With D = diag(g) S: u = beta (v - D^T k), o = D^T q + (k . q) u,
+// S = D + k u^T: the slices' partial sums of D^T k and D^T q meet once per token.  q and k
+// are made unit vectors (q also times q_scale) while a chunk is staged.
+template <typename TA, int KPT>
+__global__ void __launch_bounds__(RC_COLS * 8)
+delta_recurrence_kernel(const TA* __restrict__ q, long long ldq, const TA* __restrict__ k,
+                        long long ldk, const TA* __restrict__ v, long long ldv,
+                        const TA* __restrict__ beta_raw, long long ldb,
+                        const float* __restrict__ decay, float* __restrict__ state,
+                        const int* __restrict__ cu_q, const int* __restrict__ state_slot,
+                        float* __restrict__ out, int H, int HK, int K, int V, int KS,
+                        float unit_eps, float q_scale) {
+  extern __shared__ __align__(16) float sm[];
+  float* q_s = sm;                          // [RC_CHUNK][K]
+  float* k_s = q_s + RC_CHUNK * K;          // [RC_CHUNK][K]
+  float* g_s = k_s + RC_CHUNK * K;          // [RC_CHUNK][K]
+  float* v_s = g_s + RC_CHUNK * K;          // [RC_CHUNK][RC_COLS]
+  float* b_s = v_s + RC_CHUNK * RC_COLS;    // [RC_CHUNK] beta
+  float* kq_s = b_s + RC_CHUNK;             // [RC_CHUNK] k . q
+  float* part = kq_s + RC_CHUNK;            // [2][KS][2][RC_COLS]
+  IX_PDL_WAIT();
+  const int lane = threadIdx.x & 31, ks = threadIdx.x >> 5;
+  const int v0 = blockIdx.x * RC_COLS, h = blockIdx.y, s = blockIdx.z;
+  const int col = v0 + lane;
+  const bool col_ok = col < V;
+  const int j = h / (H / HK);
+  const int t_begin = cu_q[s], t_end = cu_q[s + 1];
+  if (t_end <= t_begin) return;
+  float* st = state + ((size_t)state_slot[s] * H + h) * K * V;
+  const int kk0 = ks * KPT;
+  float S[KPT];
+#pragma unroll
+  for (int i = 0; i < KPT; ++i) {
+    const int kk = kk0 + i;
+    S[i] = (kk < K && col_ok) ? st[(size_t)kk * V + col] : 0.f;
+  }
+  int buf = 0;
+  for (int t0 = t_begin; t0 < t_end; t0 += RC_CHUNK) {
+    const int n = min(RC_CHUNK, t_end - t0);
+    for (int i = threadIdx.x; i < n * K; i += blockDim.x) {
+      const int c = i / K, kk = i - c * K;
+      const size_t t = (size_t)(t0 + c);
+      q_s[i] = to_f32(q[t * ldq + (size_t)j * K + kk]);
+      k_s[i] = to_f32(k[t * ldk + (size_t)j * K + kk]);
+      g_s[i] = decay[(t * H + h) * K + kk];
+    }
+    for (int i = threadIdx.x; i < n * RC_COLS; i += blockDim.x) {
+      const int c = i / RC_COLS, jj = i - c * RC_COLS;
+      v_s[i] = (v0 + jj < V) ? to_f32(v[(size_t)(t0 + c) * ldv + (size_t)h * V + v0 + jj]) : 0.f;
+    }
+    if (threadIdx.x < n) {
+      const float z = to_f32(beta_raw[(size_t)(t0 + threadIdx.x) * ldb + h]);
+      b_s[threadIdx.x] = 1.0f / (1.0f + expf(-z));
+    }
+    __syncthreads();
+    // unit vectors: one warp a token; sums over lanes in strides of 32, then a shuffle tree
+    for (int c = ks; c < n; c += KS) {
+      float sq = 0.f, sk = 0.f;
+      for (int kk = lane; kk < K; kk += 32) {
+        sq = fmaf(q_s[c * K + kk], q_s[c * K + kk], sq);
+        sk = fmaf(k_s[c * K + kk], k_s[c * K + kk], sk);
+      }
+      const float iq = q_scale / sqrtf(warp_sum(sq) + unit_eps);
+      const float ik = 1.0f / sqrtf(warp_sum(sk) + unit_eps);
+      float dot = 0.f;
+      for (int kk = lane; kk < K; kk += 32) {
+        const float qq = q_s[c * K + kk] * iq, kv = k_s[c * K + kk] * ik;
+        q_s[c * K + kk] = qq;
+        k_s[c * K + kk] = kv;
+        dot = fmaf(qq, kv, dot);
+      }
+      dot = warp_sum(dot);
+      if (lane == 0) kq_s[c] = dot;
+    }
+    __syncthreads();
+    for (int c = 0; c < n; ++c) {
+      const float* qc = q_s + c * K + kk0;
+      const float* kc = k_s + c * K + kk0;
+      const float* gc = g_s + c * K + kk0;
+      float pk = 0.f, pq = 0.f;
+#pragma unroll
+      for (int i = 0; i < KPT; ++i) {
+        if (kk0 + i < K) {
+          S[i] = __fmul_rn(gc[i], S[i]);
+          pk = __fmaf_rn(S[i], kc[i], pk);
+          pq = __fmaf_rn(S[i], qc[i], pq);
+        }
+      }
+      float* pb = part + (size_t)buf * KS * 2 * RC_COLS;
+      pb[(ks * 2 + 0) * RC_COLS + lane] = pk;
+      pb[(ks * 2 + 1) * RC_COLS + lane] = pq;
+      __syncthreads();
+      float kd = 0.f, qd = 0.f;
+      for (int w = 0; w < KS; ++w) {
+        kd += pb[(w * 2 + 0) * RC_COLS + lane];
+        qd += pb[(w * 2 + 1) * RC_COLS + lane];
+      }
+      const float u = __fmul_rn(b_s[c], v_s[c * RC_COLS + lane] - kd);
+#pragma unroll
+      for (int i = 0; i < KPT; ++i)
+        if (kk0 + i < K) S[i] = __fmaf_rn(kc[i], u, S[i]);
+      if (ks == 0 && col_ok)
+        out[((size_t)(t0 + c) * H + h) * V + col] = __fmaf_rn(kq_s[c], u, qd);
+      buf ^= 1;
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < KPT; ++i) {
+    const int kk = kk0 + i;
+    if (kk < K && col_ok) st[(size_t)kk * V + col] = S[i];
+  }
+}
+
+IX_API int ix_delta_recurrence_max_dim() { return 8 * 64; }
+
+static inline int rc_slices(int K) { return K > 32 ? 8 : (K > 8 ? 4 : 1); }
+
+IX_API int ix_ssd_recurrence(const void* xbc, long long ld, const void* dt_raw, long long ld_dt,
+                             int dtype, const float* dt_bias, const float* a_log,
+                             const float* d_skip, float* state, const int* cu_q,
+                             const int* state_slot, float* out, int S, int H, int V, int K, int G,
+                             cudaStream_t stream) {
+  if (S <= 0) return IX_OK;
+  if (H <= 0 || V <= 0 || K <= 0 || G <= 0 || H % G || K > 8 * 64 || H > 65535 || S > 65535)
+    return IX_ERR_SIZE;
+  if (ld < (long long)H * V + 2LL * G * K || ld_dt < H) return IX_ERR_SIZE;
+  const int KS = rc_slices(K);
+  const int kpt = (K + KS - 1) / KS;
+  const size_t smem = ((size_t)2 * RC_CHUNK * K + RC_CHUNK * RC_COLS + RC_CHUNK +
+                       (size_t)KS * RC_CHUNK * RC_COLS) * sizeof(float);
+  if (smem > 200 * 1024) return IX_ERR_SMEM;
+  dim3 grid((V + RC_COLS - 1) / RC_COLS, H, S), block(RC_COLS * KS);
+#define SSD_GO(KPT)                                                                          \
+  IX_DISPATCH_DTYPE(dtype, TA, {                                                             \
+    auto kern = ssd_recurrence_kernel<TA, KPT>;                                              \
+    if (smem > 48 * 1024)                                                                    \
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
+    ix_launch(kern, grid, block, smem, stream, (const TA*)xbc, ld, (const TA*)dt_raw, ld_dt, \
+              dt_bias, a_log, d_skip, state, cu_q, state_slot, out, H, V, K, G, KS);         \
+  })
+  if (kpt <= 8) SSD_GO(8);
+  else if (kpt <= 16) SSD_GO(16);
+  else if (kpt <= 32) SSD_GO(32);
+  else SSD_GO(64);
+#undef SSD_GO
+  return ix_launch_status();
+}
+
+IX_API int ix_delta_recurrence(const void* q, long long ldq, const void* k, long long ldk,
+                               const void* v, long long ldv, const void* beta_raw, long long ldb,
+                               int dtype, const float* decay, float* state, const int* cu_q,
+                               const int* state_slot, float* out, int S, int H, int HK, int K,
+                               int V, float unit_eps, float q_scale, cudaStream_t stream) {
+  if (S <= 0) return IX_OK;
+  if (H <= 0 || HK <= 0 || H % HK || K <= 0 || V <= 0 || K > 8 * 64 || H > 65535 || S > 65535)
+    return IX_ERR_SIZE;
+  if (ldq < (long long)HK * K || ldk < (long long)HK * K || ldv < (long long)H * V || ldb < H)
+    return IX_ERR_SIZE;
+  const int KS = rc_slices(K);
+  const int kpt = (K + KS - 1) / KS;
+  const size_t smem = ((size_t)3 * RC_CHUNK * K + RC_CHUNK * RC_COLS + 2 * RC_CHUNK +
+                       (size_t)2 * KS * 2 * RC_COLS) * sizeof(float);
+  if (smem > 200 * 1024) return IX_ERR_SMEM;
+  dim3 grid((V + RC_COLS - 1) / RC_COLS, H, S), block(RC_COLS * KS);
+#define DR_GO(KPT)                                                                           \
+  IX_DISPATCH_DTYPE(dtype, TA, {                                                             \
+    auto kern = delta_recurrence_kernel<TA, KPT>;                                            \
+    if (smem > 48 * 1024)                                                                    \
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
+    ix_launch(kern, grid, block, smem, stream, (const TA*)q, ldq, (const TA*)k, ldk,         \
+              (const TA*)v, ldv, (const TA*)beta_raw, ldb, decay, state, cu_q, state_slot,   \
+              out, H, HK, K, V, KS, unit_eps, q_scale);                                      \
+  })
+  if (kpt <= 8) DR_GO(8);
+  else if (kpt <= 16) DR_GO(16);
+  else if (kpt <= 32) DR_GO(32);
+  else DR_GO(64);
+#undef DR_GO
+  return ix_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// gate + group norm: out = groupnorm(y * silu(z)) * gain.  One block per (token, group).
+// ---------------------------------------------------------------------------
+template <typename TA>
+__global__ void gated_group_norm_kernel(const float* __restrict__ y, const TA* __restrict__ z,
+                                        long long ldz, const float* __restrict__ gain,
+                                        TA* __restrict__ out, int W, int groups, float eps) {
+  __shared__ float scratch[32];
+  IX_PDL_WAIT();
+  const int t = blockIdx.x, g = blockIdx.y;
+  const int n = W / groups, c0 = g * n;
+  const float* yr = y + (size_t)t * W + c0;
+  const TA* zr = z + (size_t)t * ldz + c0;
+  float sq = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float zz = to_f32(zr[i]);
+    const float v = yr[i] * (zz / (1.0f + expf(-zz)));
+    sq += v * v;
+  }
+  const float inv = 1.0f / sqrtf(block_sum(sq, scratch) / (float)n + eps);
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float zz = to_f32(zr[i]);
+    const float v = yr[i] * (zz / (1.0f + expf(-zz)));
+    out[(size_t)t * W + c0 + i] = from_f32<TA>(v * inv * gain[c0 + i]);
+  }
+}
+
+IX_API int ix_gated_group_norm(const float* y, const void* z, int dtype, long long ldz,
+                               const float* gain, void* out, int T, int W, int groups, float eps,
+                               cudaStream_t stream) {
+  if (T <= 0) return IX_OK;
+  if (W <= 0 || groups <= 0 || W % groups || ldz < W || groups > 65535) return IX_ERR_SIZE;
+  const int n = W / groups;
+  const int threads = n >= 1024 ? 256 : (n >= 256 ? 128 : 64);
+  IX_DISPATCH_DTYPE(dtype, TA,
+                    ix_launch(gated_group_norm_kernel<TA>, dim3(T, groups), dim3(threads), 0,
+                              stream, y, (const TA*)z, ldz, gain, (TA*)out, W, groups, eps));
+  return ix_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// normed pair mean: out = (l / rms(l) * gl + r / rms(r) * gr) / 2, all fp32.
+// ---------------------------------------------------------------------------
+template <typename TL>
+__global__ void normed_pair_mean_kernel(const TL* __restrict__ l, const TL* __restrict__ r,
+                                        const float* __restrict__ gl,
+                                        const float* __restrict__ gr, float* __restrict__ out,
+                                        int W, float eps) {
+  __shared__ float scratch[32];
+  IX_PDL_WAIT();
+  const int t = blockIdx.x;
+  const TL* lr = l + (size_t)t * W;
+  const TL* rr = r + (size_t)t * W;
+  float sl = 0.f, sr = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float a = to_f32(lr[i]), b = to_f32(rr[i]);
+    sl += a * a;
+    sr += b * b;
+  }
+  const float il = 1.0f / sqrtf(block_sum(sl, scratch) / (float)W + eps);
+  const float ir = 1.0f / sqrtf(block_sum(sr, scratch) / (float)W + eps);
+  for (int i = threadIdx.x; i < W; i += blockDim.x)
+    out[(size_t)t * W + i] = 0.5f * (to_f32(lr[i]) * il * gl[i] + to_f32(rr[i]) * ir * gr[i]);
+}
+
+IX_API int ix_normed_pair_mean(const void* l, const void* r, int dtype, const float* gl,
+                               const float* gr, float* out, int T, int W, float eps,
+                               cudaStream_t stream) {
+  if (T <= 0) return IX_OK;
+  if (W <= 0) return IX_ERR_SIZE;
+  const int threads = W >= 2048 ? 512 : (W >= 512 ? 256 : 128);
+  IX_DISPATCH_DTYPE(dtype, TL,
+                    ix_launch(normed_pair_mean_kernel<TL>, dim3(T), dim3(threads), 0, stream,
+                              (const TL*)l, (const TL*)r, gl, gr, out, W, eps));
+  return ix_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// relu squared; table routing; rows times a constant.
+// ---------------------------------------------------------------------------
+template <typename TA>
+__global__ void relu_squared_kernel(const TA* __restrict__ x, TA* __restrict__ out, size_t n) {
+  IX_PDL_WAIT();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (size_t)gridDim.x * blockDim.x) {
+    const float v = fmaxf(to_f32(x[i]), 0.f);
+    out[i] = from_f32<TA>(v * v);
+  }
+}
+
+IX_API int ix_relu_squared(const void* x, void* out, int dtype, long long n,
+                           cudaStream_t stream) {
+  if (n <= 0) return IX_OK;
+  const long long want = (n + 255) / 256;
+  const int blocks = (int)(want > 148 * 16 ? 148 * 16 : want);
+  IX_DISPATCH_DTYPE(dtype, TA,
+                    ix_launch(relu_squared_kernel<TA>, dim3(blocks), dim3(256), 0, stream,
+                              (const TA*)x, (TA*)out, (size_t)n));
+  return ix_launch_status();
+}
+
+__global__ void table_route_kernel(const int* __restrict__ ids, const int* __restrict__ table,
+                                   int* __restrict__ idx, float* __restrict__ wts, int T, int top,
+                                   int vocab, int experts) {
+  IX_PDL_WAIT();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= T * top) return;
+  const int t = i / top, j = i - t * top;
+  const int id = min(max(ids[t], 0), vocab - 1);
+  idx[i] = min(max(table[(size_t)id * top + j], 0), experts - 1);
+  wts[i] = 1.0f / (float)top;
+}
+
+IX_API int ix_table_route(const int* ids, const int* table, int* idx, float* wts, int T, int top,
+                          int vocab, int experts, cudaStream_t stream) {
+  if (T <= 0) return IX_OK;
+  if (top <= 0 || vocab <= 0 || experts <= 0) return IX_ERR_SIZE;
+  const int n = T * top;
+  ix_launch(table_route_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, ids, table, idx, wts,
+            T, top, vocab, experts);
+  return ix_launch_status();
+}
+
+__global__ void scale_rows_kernel(float* __restrict__ x, float scale, size_t n) {
+  IX_PDL_WAIT();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (size_t)gridDim.x * blockDim.x)
+    x[i] *= scale;
+}
+
+IX_API int ix_scale_rows(float* x, float scale, long long n, cudaStream_t stream) {
+  if (n <= 0) return IX_OK;
+  const long long want = (n + 255) / 256;
+  const int blocks = (int)(want > 148 * 16 ? 148 * 16 : want);
+  ix_launch(scale_rows_kernel, dim3(blocks), dim3(256), 0, stream, x, scale, (size_t)n);
+  return ix_launch_status();
+}

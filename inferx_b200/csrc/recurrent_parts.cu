@@ -6,6 +6,7 @@
 //   low-rank decay     z[t][c] = b[c] + sum_r act(x[t][r]) * w2t[r][c], then
 //                        form 0:  exp(-exp(z)),            act = tanh
 //                        form 1:  sigmoid(z)^(1/tau),       act = identity
+//                        form 2:  exp(-exp(A[c / per_head]) * softplus(z)), act = identity
 //   linear recurrence  per (sequence, head), tokens in order, S [K][V] in fp32:
 //                        plain form:  S = diag(w_t) S + k_t v_t^T;  o_t = S^T q_t
 //                        bonus form:  o_t = (S + diag(u) k_t v_t^T)^T q_t;
@@ -117,7 +118,8 @@ template <typename TX>
 __global__ void lowrank_decay_kernel(const TX* __restrict__ x, long long ldx,
                                      const float* __restrict__ w2t, const float* __restrict__ b,
                                      float* __restrict__ out, int T, int C, int R, int form,
-                                     float inv_tau) {
+                                     float inv_tau, const float* __restrict__ head_param,
+                                     int per_head) {
   extern __shared__ __align__(16) float act[];   // [LRD_TOKENS][R]
   IX_PDL_WAIT();
   const int t0 = blockIdx.x * LRD_TOKENS;
@@ -156,6 +158,7 @@ __global__ void lowrank_decay_kernel(const TX* __restrict__ x, long long ldx,
     }
   }
   const float bias = b ? b[c] : 0.f;
+  const float neg_rate = form == 2 ? -expf(head_param[c / per_head]) : 0.f;
 #pragma unroll
   for (int j = 0; j < LRD_TOKENS; ++j) {
     if (j >= nt) break;
@@ -163,6 +166,8 @@ __global__ void lowrank_decay_kernel(const TX* __restrict__ x, long long ldx,
     float d;
     if (form == 0) {
       d = expf(-expf(v));
+    } else if (form == 2) {
+      d = expf(neg_rate * (v > 20.f ? v : log1pf(expf(v))));
     } else {
       // log sigmoid(v) = min(v, 0) - log(1 + exp(-|v|))
       d = expf((fminf(v, 0.f) - log1pf(expf(-fabsf(v)))) * inv_tau);
@@ -173,16 +178,18 @@ __global__ void lowrank_decay_kernel(const TX* __restrict__ x, long long ldx,
 
 IX_API int ix_lowrank_decay(const void* x, int x_dtype, long long ldx, const float* w2t,
                             const float* b, float* out, int T, int C, int R, int form, float tau,
-                            cudaStream_t stream) {
+                            const float* head_param, int per_head, cudaStream_t stream) {
   if (T <= 0) return IX_OK;
-  if (C <= 0 || R <= 0 || ldx < R || (form != 0 && form != 1) || !(tau > 0.f)) return IX_ERR_SIZE;
+  if (C <= 0 || R <= 0 || ldx < R || form < 0 || form > 2 || !(tau > 0.f)) return IX_ERR_SIZE;
+  if (form == 2 && (!head_param || per_head <= 0 || C % per_head)) return IX_ERR_SIZE;
   const size_t smem = (size_t)LRD_TOKENS * R * sizeof(float);
   if (smem > 48 * 1024) return IX_ERR_SMEM;
   dim3 grid((T + LRD_TOKENS - 1) / LRD_TOKENS, (C + LRD_THREADS - 1) / LRD_THREADS);
   if (grid.y > 65535) return IX_ERR_SIZE;
   IX_DISPATCH_DTYPE(x_dtype, TX,
                     ix_launch(lowrank_decay_kernel<TX>, grid, dim3(LRD_THREADS), smem, stream,
-                              (const TX*)x, ldx, w2t, b, out, T, C, R, form, 1.0f / tau));
+                              (const TX*)x, ldx, w2t, b, out, T, C, R, form, 1.0f / tau,
+                              head_param, per_head));
   return ix_launch_status();
 }
 
@@ -540,7 +547,7 @@ IX_API int ix_linear_recurrence(const void* q, long long ldq, const void* k, lon
 
 // ---------------------------------------------------------------------------
 // head norm + gate.  One warp per (token, head).  `gain` covers all heads
-// (gain_per_head) or is shared by them.
+// (gain_per_head) or is shared by them.  gate_form 0: silu(gate); 1: sigmoid(gate).
 // ---------------------------------------------------------------------------
 #define HNG_WARPS 4
 
@@ -548,7 +555,7 @@ template <typename TG, typename TA>
 __global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ gain,
                                       int gain_per_head, const TG* __restrict__ gate,
                                       long long ldg, TA* __restrict__ out, int H, int V,
-                                      float eps) {
+                                      float eps, int gate_form) {
   IX_PDL_WAIT();
   const int t = blockIdx.x;
   const int h = blockIdx.y * HNG_WARPS + (threadIdx.x >> 5);
@@ -563,7 +570,8 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* 
   TA* dst = out + ((size_t)t * H + h) * V;
   for (int c = lane; c < V; c += 32) {
     const float z = to_f32(gt[c]);
-    dst[c] = from_f32<TA>(row[c] * inv * g[c] * (z / (1.0f + expf(-z))));
+    const float sg = 1.0f / (1.0f + expf(-z));
+    dst[c] = from_f32<TA>(row[c] * inv * g[c] * (gate_form ? sg : z * sg));
   }
 }
 
@@ -606,7 +614,7 @@ __global__ void head_norm_gate_bf16_vec_kernel(const float* __restrict__ o,
 
 IX_API int ix_head_norm_gate(const float* o, const float* gain, int gain_per_head,
                              const void* gate, int gate_dtype, long long ldg, void* out,
-                             int out_dtype, int T, int H, int V, float eps,
+                             int out_dtype, int T, int H, int V, float eps, int gate_form,
                              cudaStream_t stream) {
   if (T <= 0) return IX_OK;
   if (H <= 0 || V <= 0 || ldg < (long long)H * V) return IX_ERR_SIZE;
@@ -614,7 +622,7 @@ IX_API int ix_head_norm_gate(const float* o, const float* gain, int gain_per_hea
   if (groups > 65535) return IX_ERR_SIZE;
   if (gate_dtype != out_dtype) return IX_ERR_UNSUPPORTED;
   const int gl = V / 4;
-  if (out_dtype == IX_BF16 && V % 4 == 0 && gl <= 32 && (gl & (gl - 1)) == 0 && ldg % 4 == 0 &&
+  if (gate_form == 0 && out_dtype == IX_BF16 && V % 4 == 0 && gl <= 32 && (gl & (gl - 1)) == 0 && ldg % 4 == 0 &&
       (((uintptr_t)o | (uintptr_t)gain) & 15) == 0 && (((uintptr_t)gate | (uintptr_t)out) & 7) == 0) {
     const int hpb = HNG_WARPS * (32 / gl);
     const int vgroups = (H + hpb - 1) / hpb;
@@ -633,6 +641,6 @@ IX_API int ix_head_norm_gate(const float* o, const float* gain, int gain_per_hea
   IX_DISPATCH_DTYPE(out_dtype, TA,
                     ix_launch(head_norm_gate_kernel<TA, TA>, dim3(T, groups),
                               dim3(32 * HNG_WARPS), 0, stream, o, gain, gain_per_head,
-                              (const TA*)gate, ldg, (TA*)out, H, V, eps));
+                              (const TA*)gate, ldg, (TA*)out, H, V, eps, gate_form));
   return ix_launch_status();
 }

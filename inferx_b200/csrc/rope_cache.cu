@@ -21,7 +21,8 @@ __global__ void qkv_rope_append_kernel(const TA* __restrict__ qkv, const float* 
                                        const int* __restrict__ slots, TA* __restrict__ q_out,
                                        TA* __restrict__ k_cache, TA* __restrict__ v_cache,
                                        int page_size, TA* __restrict__ k_out,
-                                       TA* __restrict__ v_out, int heads, int kvh, int hd) {
+                                       TA* __restrict__ v_out, int heads, int kvh, int hd,
+                                       int vd) {
   extern __shared__ float trig[];  // cos[rot/2], sin[rot/2]
   const int t = blockIdx.x;
   const int half = rot >> 1;
@@ -36,7 +37,7 @@ __global__ void qkv_rope_append_kernel(const TA* __restrict__ qkv, const float* 
   }
   __syncthreads();
 
-  const int width = (heads + 2 * kvh) * hd;
+  const int width = (heads + kvh) * hd + kvh * vd;   // value heads may have a size of their own
   const TA* in = qkv + (size_t)t * width;
   const int slot = slots ? slots[t] : -1;
   const int page = slot >= 0 ? slot / page_size : 0;
@@ -69,17 +70,17 @@ __global__ void qkv_rope_append_kernel(const TA* __restrict__ qkv, const float* 
     }
   }
   // V heads: bias only
-  const int v_elems = kvh * hd;
+  const int v_elems = kvh * vd;
   const int vbase = (heads + kvh) * hd;
   for (int idx = threadIdx.x; idx < v_elems; idx += blockDim.x) {
-    const int kh = idx / hd;
-    const int d = idx - kh * hd;
+    const int kh = idx / vd;
+    const int d = idx - kh * vd;
     float x = to_f32(in[vbase + idx]);
     if (bias) x += bias[vbase + idx];
     const TA v = from_f32<TA>(x);
     if (v_out) v_out[(size_t)t * v_elems + idx] = v;
     if (slot >= 0 && v_cache)
-      v_cache[(((size_t)page * kvh + kh) * page_size + off) * hd + d] = v;
+      v_cache[(((size_t)page * kvh + kh) * page_size + off) * vd + d] = v;
   }
 }
 
@@ -183,16 +184,16 @@ IX_API int ix_qkv_rope_append(const void* qkv, const float* bias, const int* pos
                               const float* inv_freq, int rot, const int* slots, void* q_out,
                               void* k_cache, void* v_cache, int page_size, void* k_out,
                               void* v_out, int act_dtype, int T, int heads, int kvh, int hd,
-                              cudaStream_t stream) {
+                              int vd, cudaStream_t stream) {
   if (T <= 0) return IX_OK;
-  if (heads <= 0 || kvh <= 0 || hd <= 0 || page_size <= 0) return IX_ERR_SIZE;
+  if (heads <= 0 || kvh <= 0 || hd <= 0 || vd <= 0 || page_size <= 0) return IX_ERR_SIZE;
   if (rot < 0 || rot > hd || (rot & 1)) return IX_ERR_SIZE;
   if (rot > 0 && inv_freq == nullptr) return IX_ERR_SIZE;
   const size_t smem = (size_t)rot * sizeof(float);
   if (smem > 48 * 1024) return IX_ERR_SMEM;
   const uintptr_t all = (uintptr_t)qkv | (uintptr_t)bias | (uintptr_t)q_out | (uintptr_t)k_cache |
                         (uintptr_t)v_cache | (uintptr_t)k_out | (uintptr_t)v_out;
-  if (act_dtype == IX_BF16 && hd % 8 == 0 && rot % 16 == 0 && (all & 15) == 0) {
+  if (act_dtype == IX_BF16 && vd == hd && hd % 8 == 0 && rot % 16 == 0 && (all & 15) == 0) {
     const int items = (heads + kvh) * (rot / 16 + (hd - rot) / 8) + kvh * (hd / 8);
     const int threads = items >= 256 ? 256 : (items >= 128 ? 128 : 64);
     ix_launch(qkv_rope_append_bf16_vec_kernel, dim3(T), dim3(threads), smem, stream,
@@ -205,7 +206,7 @@ IX_API int ix_qkv_rope_append(const void* qkv, const float* bias, const int* pos
                     (qkv_rope_append_kernel<TA><<<T, 256, smem, stream>>>(
                         (const TA*)qkv, bias, positions, inv_freq, rot, slots, (TA*)q_out,
                         (TA*)k_cache, (TA*)v_cache, page_size, (TA*)k_out, (TA*)v_out, heads, kvh,
-                        hd)));
+                        hd, vd)));
   return ix_launch_status();
 }
 

@@ -294,17 +294,21 @@ def qkv_rope_append(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: 
                     inv_freq: Optional[torch.Tensor], rotary_dim: int, heads: int, kv_heads: int,
                     head_dim: int, k_cache: Optional[torch.Tensor],
                     v_cache: Optional[torch.Tensor], slots: Optional[torch.Tensor],
-                    want_dense_kv: bool = False):
+                    want_dense_kv: bool = False, value_dim: int = 0):
     """Split + bias + rotate; returns q [T,heads,hd] (and dense k, v when asked);
-    writes k, v into the paged cache at ``slots`` when a cache is given."""
+    writes k, v into the paged cache at ``slots`` when a cache is given.  ``value_dim``:
+    the size of a value head when it differs from ``head_dim`` (the row is then
+    q | k | v with v of kv_heads * value_dim, and the value pages are that wide)."""
     _chk("qkv", qkv)
     _chk("bias", bias, torch.float32, optional=True)
     _chk("positions", positions, torch.int32)
     _chk("inv_freq", inv_freq, torch.float32, optional=True)
     _chk("slots", slots, torch.int32, optional=True)
     T, width = qkv.shape
-    if width != (heads + 2 * kv_heads) * head_dim:
-        raise KernelError(f"qkv_rope_append: row width {width} is not (heads+2*kv_heads)*head_dim")
+    vd = value_dim or head_dim
+    if width != (heads + kv_heads) * head_dim + kv_heads * vd:
+        raise KernelError(f"qkv_rope_append: row width {width} is not (heads+kv_heads)*head_dim "
+                          "+ kv_heads*value_dim")
     if bias is not None and bias.numel() != width:
         raise KernelError("qkv_rope_append: bias length does not match the fused row")
     if rotary_dim and (inv_freq is None or inv_freq.numel() != rotary_dim // 2):
@@ -316,17 +320,18 @@ def qkv_rope_append(qkv: torch.Tensor, bias: Optional[torch.Tensor], positions: 
         if slots is None:
             raise KernelError("qkv_rope_append: a cache needs slots")
         P, ckv, page_size, chd = k_cache.shape
-        if ckv != kv_heads or chd != head_dim or v_cache.shape != k_cache.shape:
+        if ckv != kv_heads or chd != head_dim or \
+                tuple(v_cache.shape) != (P, ckv, page_size, vd):
             raise KernelError("qkv_rope_append: cache geometry does not match the heads")
     q = torch.empty((T, heads, head_dim), dtype=qkv.dtype, device=qkv.device)
     k = v = None
     if want_dense_kv:
         k = torch.empty((T, kv_heads, head_dim), dtype=qkv.dtype, device=qkv.device)
-        v = torch.empty_like(k)
+        v = torch.empty((T, kv_heads, vd), dtype=qkv.dtype, device=qkv.device)
     code = _lib().ix_qkv_rope_append(
         _ptr(qkv), _ptr(bias), _ptr(positions), _ptr(inv_freq), rotary_dim, _ptr(slots), _ptr(q),
         _ptr(k_cache), _ptr(v_cache), page_size, _ptr(k), _ptr(v), _dtype_code(qkv), T, heads,
-        kv_heads, head_dim, _stream())
+        kv_heads, head_dim, vd, _stream())
     _check(code, "qkv_rope_append")
     _count()
     return (q, k, v) if want_dense_kv else q
@@ -393,12 +398,13 @@ def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
     _chk("positions", positions, torch.int32)
     T, heads, hd = q.shape
     P, kvh, page, chd = k_cache.shape
-    if chd != hd:
+    vd = v_cache.shape[3]
+    if chd != hd or tuple(v_cache.shape[:3]) != (P, kvh, page):
         raise KernelError("paged_attention: cache head size differs from the query's")
-    out = torch.empty_like(q)
+    out = torch.empty((T, heads, vd), dtype=q.dtype, device=q.device)
     code = _lib().ix_paged_attention_generic(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(seq_of_token),
-        _ptr(positions), _ptr(out), _dtype_code(q), T, heads, kvh, hd, page,
+        _ptr(positions), _ptr(out), _dtype_code(q), T, heads, kvh, hd, vd, page,
         block_table.shape[1], window, ctypes.c_float(scale), ctypes.c_float(softcap), _stream())
     _check(code, "paged_attention_generic")
     _count()
@@ -411,7 +417,8 @@ def paged_attention_tiled(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch
     """CUDA-core attention for a ragged batch, tiled (32 queries of a sequence against 64
     keys at a time in shared memory, fp32 math): sequence s brings the queries
     q[cu_q[s]:cu_q[s+1]] at positions q_pos0[s], q_pos0[s]+1, ...  Any element type, head
-    sizes that are a multiple of 4 up to 256."""
+    sizes that are a multiple of 4 up to 256; the value pages may have a head size of
+    their own (the output then has it)."""
     _chk("q", q)
     _chk("k_cache", k_cache, q.dtype)
     _chk("v_cache", v_cache, q.dtype)
@@ -421,14 +428,15 @@ def paged_attention_tiled(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch
     T, heads, hd = q.shape
     P, kvh, page, chd = k_cache.shape
     S = q_pos0.numel()
-    if chd != hd or v_cache.shape != k_cache.shape:
+    vd = v_cache.shape[3]
+    if chd != hd or tuple(v_cache.shape[:3]) != (P, kvh, page):
         raise KernelError("paged_attention_tiled: cache geometry differs from the query's")
     if cu_q.numel() != S + 1 or block_table.shape[0] != S:
         raise KernelError("paged_attention_tiled: cu_q, q_pos0 and block_table disagree")
-    out = torch.empty_like(q)
+    out = torch.empty((T, heads, vd), dtype=q.dtype, device=q.device)
     code = _lib().ix_paged_attention_tiled(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(cu_q), _ptr(q_pos0),
-        _ptr(out), _dtype_code(q), T, S, heads, kvh, hd, page, block_table.shape[1], window,
+        _ptr(out), _dtype_code(q), T, S, heads, kvh, hd, vd, page, block_table.shape[1], window,
         ctypes.c_float(scale), ctypes.c_float(softcap), _stream())
     _check(code, "paged_attention_tiled")
     _count()
@@ -776,9 +784,11 @@ def paged_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
 
 def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                     block_table: torch.Tensor, step, window: int, scale: float,
-                    softcap: float = 0.0):
+                    softcap: float = 0.0, fp32_weights: bool = False):
     """Causal attention of this step's queries over the paged cache.  With ``softcap``
-    > 0 a score s becomes softcap * tanh(s / softcap) before the softmax.
+    > 0 a score s becomes softcap * tanh(s / softcap) before the softmax.  With
+    ``fp32_weights``, or value pages whose head size differs from the keys', the
+    fp32-arithmetic kernels run whatever the element type.
 
     ``step`` carries the batch description (``seq_of_token``, ``positions``, ``cu_q``,
     ``q_pos0``, ``kv_len``, ``max_q_len``, ``max_kv_len``, ``all_decode``).  Steps of
@@ -786,6 +796,9 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     tuned kernels do not take, to the general kernel."""
     hd = q.shape[2]
     page = k_cache.shape[2]
+    if fp32_weights or v_cache.shape[3] != hd:
+        return _paged_attention_softcap(q, k_cache, v_cache, block_table, step, window, scale,
+                                        softcap)
     if softcap > 0 and not (scale > 0 and USE_TMA_DECODE and _tma_decode_applies(q, page)
                             and USE_TCGEN05_ATTENTION and _tc_prefill_applies(q, page)):
         # of the tuned kernels only the TMA decode form and the tcgen05 prompt form squash
@@ -819,10 +832,11 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
 
 
 def _paged_attention_softcap(q, k_cache, v_cache, block_table, step, window, scale, softcap):
-    """Attention with squashed scores: the fp32-arithmetic kernels."""
+    """The fp32-arithmetic kernels (squashed scores or not)."""
     hd = q.shape[2]
     if (step.num_tokens >= TILED_ATTENTION_MIN_QUERIES * step.num_seqs
             and _lib().ix_paged_attention_tiled_applies(hd)
+            and _lib().ix_paged_attention_tiled_applies(v_cache.shape[3])
             and getattr(step, "cu_q", None) is not None):
         return paged_attention_tiled(q, k_cache, v_cache, block_table, step.cu_q, step.q_pos0,
                                      window, scale, softcap)
@@ -1430,26 +1444,36 @@ def shift_mix(x: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, step):
     return out
 
 
-_DECAY_FORMS = {"exp_exp_tanh": 0, "sigmoid_root": 1}
+_DECAY_FORMS = {"exp_exp_tanh": 0, "sigmoid_root": 1, "exp_rate_softplus": 2}
 
 
 def lowrank_decay(x: torch.Tensor, w2t: torch.Tensor, b: Optional[torch.Tensor], mode: str,
-                  tau: float = 1.0):
+                  tau: float = 1.0, head_log_rate: Optional[torch.Tensor] = None):
     """fp32 [T, C] decays from the inner activations ``x`` [T, R] of a low-rank product
     (a view with unit inner stride): z = act(x) . w2t + b with the outer matrix transposed,
     ``w2t`` fp32 [R, C], then "exp_exp_tanh": exp(-exp(z)) with act = tanh; "sigmoid_root":
-    sigmoid(z)^(1/tau) with act the identity."""
+    sigmoid(z)^(1/tau) with act the identity; "exp_rate_softplus": exp(-exp(A_h) *
+    softplus(z)) with act the identity, where ``head_log_rate`` fp32 [heads] holds A and
+    the C channels are split evenly over the heads."""
     _chk("w2t", w2t, torch.float32)
+    _chk("head_log_rate", head_log_rate, torch.float32, optional=True)
     _chk("b", b, torch.float32, optional=True)
     if mode not in _DECAY_FORMS:
         raise KernelError(f"lowrank_decay: unknown form {mode!r}; known: {sorted(_DECAY_FORMS)}")
     R, C = w2t.shape
     ldx = _row_view("lowrank_decay: x", x, R)
     T = x.shape[0]
+    per_head = 0
+    if mode == "exp_rate_softplus":
+        if head_log_rate is None or C % head_log_rate.numel():
+            raise KernelError("lowrank_decay: this form needs a rate per head that splits "
+                              "the channels evenly")
+        per_head = C // head_log_rate.numel()
     out = torch.empty((T, C), dtype=torch.float32, device=x.device)
     _check(_lib().ix_lowrank_decay(_ptr(x), _dtype_code(x), ctypes.c_longlong(ldx), _ptr(w2t),
                                    _ptr(b), _ptr(out), T, C, R, _DECAY_FORMS[mode],
-                                   ctypes.c_float(tau), _stream()), "lowrank_decay")
+                                   ctypes.c_float(tau), _ptr(head_log_rate), per_head,
+                                   _stream()), "lowrank_decay")
     _count()
     return out
 
@@ -1521,9 +1545,13 @@ def check_recurrence_limits(dim: int, where: str = ""):
                           f"kernel's {most}")
 
 
+_GATE_FORMS = {"silu": 0, "sigmoid": 1}
+
+
 def head_norm_gate(o: torch.Tensor, gain: torch.Tensor, gate: torch.Tensor, eps: float,
-                   out_dtype: torch.dtype):
-    """out[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * gain * silu(gate[t, h]) for
+                   out_dtype: torch.dtype, gate_form: str = "silu"):
+    """out[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * gain * act(gate[t, h]) (act:
+    silu, or sigmoid with ``gate_form`` "sigmoid") for
     o fp32 [T, heads, vdim]; ``gain`` fp32 [vdim] (shared by the heads) or [heads * vdim];
     ``gate`` a view [T, heads * vdim] with unit inner stride in ``out_dtype``."""
     _chk("o", o, torch.float32)
@@ -1536,6 +1564,226 @@ def head_norm_gate(o: torch.Tensor, gain: torch.Tensor, gate: torch.Tensor, eps:
     _check(_lib().ix_head_norm_gate(
         _ptr(o), _ptr(gain), 1 if (gain.numel() == H * V and H > 1) else 0, _ptr(gate),
         _dtype_code(gate), ctypes.c_longlong(ldg), _ptr(out), _dtype_code(out), T, H, V,
-        ctypes.c_float(eps), _stream()), "head_norm_gate")
+        ctypes.c_float(eps), _GATE_FORMS[gate_form], _stream()), "head_norm_gate")
     _count()
     return out
+
+
+# ---------------------------------------------------------------------------
+# Faces of csrc/delta_parts.cu
+def add_scaled_norm(resid: torch.Tensor, delta, delta_scale: float,
+                    vector: Optional[torch.Tensor], gain: torch.Tensor, eps: float,
+                    out_dtype: torch.dtype, center: bool = True,
+                    rows: Optional[torch.Tensor] = None):
+    """resid += delta_scale * delta + vector (kept when ``rows`` is None), then the norm of
+    the rows times ``gain``: with ``center`` (x - mean) / sqrt(mean((x - mean)^2) + eps),
+    else x / sqrt(mean(x^2) + eps).  ``delta`` [T, H] fp32 or bfloat16 (or not yet written:
+    anything with ``materialize``), ``vector`` fp32 [H]; either may be None.  With ``rows``
+    the listed rows are gathered, normalised and returned without writing the residual."""
+    if hasattr(delta, "materialize"):
+        delta = delta.materialize()
+    _chk("resid", resid, torch.float32)
+    _chk("gain", gain, torch.float32)
+    _chk("delta", delta, optional=True)
+    _chk("vector", vector, torch.float32, optional=True)
+    _chk("rows", rows, torch.int32, optional=True)
+    T, H = resid.shape
+    if gain.numel() != H or (vector is not None and vector.numel() != H):
+        raise KernelError("add_scaled_norm: gain or vector do not fit the rows")
+    if delta is not None and delta.shape != resid.shape:
+        raise KernelError("add_scaled_norm: delta must have the residual's shape")
+    R = T if rows is None else rows.numel()
+    out = torch.empty((R, H), dtype=out_dtype, device=resid.device)
+    _check(_lib().ix_add_scaled_norm(
+        _ptr(resid), _ptr(delta), _dtype_code(delta) if delta is not None else F32,
+        ctypes.c_float(delta_scale), _ptr(vector), _ptr(gain), _ptr(rows), _ptr(out),
+        _dtype_code(out), R, H, ctypes.c_float(eps), 1 if center else 0,
+        1 if rows is None and (delta is not None or vector is not None) else 0, _stream()),
+        "add_scaled_norm")
+    _count()
+    return out
+
+
+def stream_concat(resid: torch.Tensor, delta, delta_scale: float,
+                  vector: Optional[torch.Tensor], first: torch.Tensor, out_dtype: torch.dtype):
+    """[T, 2 H] in ``out_dtype``: row t is [resid[t] + delta_scale * delta[t] + vector ;
+    first[t]] (``resid`` and ``first`` fp32 [T, H]; ``resid`` is not written)."""
+    if hasattr(delta, "materialize"):
+        delta = delta.materialize()
+    _chk("resid", resid, torch.float32)
+    _chk("first", first, torch.float32)
+    _chk("delta", delta, optional=True)
+    _chk("vector", vector, torch.float32, optional=True)
+    T, H = resid.shape
+    if first.shape != resid.shape or (delta is not None and delta.shape != resid.shape):
+        raise KernelError("stream_concat: the tensors must have the residual's shape")
+    out = torch.empty((T, 2 * H), dtype=out_dtype, device=resid.device)
+    _check(_lib().ix_stream_concat(
+        _ptr(resid), _ptr(delta), _dtype_code(delta) if delta is not None else F32,
+        ctypes.c_float(delta_scale), _ptr(vector), _ptr(first), _ptr(out), _dtype_code(out), T, H,
+        _stream()), "stream_concat")
+    _count()
+    return out
+
+
+def causal_conv(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
+                state: torch.Tensor, step, silu: bool = True):
+    """Causal convolution over time per channel with the activation: x [T, C] (a view with
+    unit inner stride), ``w`` fp32 [C, taps] whose last column multiplies the current
+    token, ``bias`` fp32 [C] or None, ``state`` fp32 [slots, taps - 1, C]: a request's last
+    taps - 1 inputs, read for the tokens before this step's first and moved on.  Returns
+    [T, C] in x's element type."""
+    _chk("w", w, torch.float32)
+    _chk("bias", bias, torch.float32, optional=True)
+    _chk("state", state, torch.float32)
+    C, taps = w.shape
+    ldx = _row_view("causal_conv: x", x, C)
+    T = x.shape[0]
+    if tuple(state.shape[1:]) != (taps - 1, C) or (bias is not None and bias.numel() != C):
+        raise KernelError("causal_conv: state or bias do not fit the channels and taps")
+    out = torch.empty((T, C), dtype=x.dtype, device=x.device)
+    _check(_lib().ix_causal_conv(
+        _ptr(x), _dtype_code(x), ctypes.c_longlong(ldx), _ptr(w), _ptr(bias), _ptr(state),
+        _ptr(step.cu_q), _ptr(step.seq_of_token), _ptr(step.state_slot), _ptr(out), T,
+        step.num_seqs, C, taps, 1 if silu else 0, _stream()), "causal_conv")
+    _count(2 if taps > 1 else 1)
+    return out
+
+
+def ssd_recurrence(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor,
+                   a_log: torch.Tensor, d_skip: torch.Tensor, state: torch.Tensor, step,
+                   heads: int, vdim: int, nstate: int, groups: int):
+    """State-space recurrence with a scalar decay per head.  ``xbc`` [T, heads * vdim +
+    2 groups * nstate] holds x | B | C; ``dt_raw`` [T, heads] (a view) the step sizes
+    before their bias and softplus; ``state`` fp32 [slots, heads, nstate, vdim], updated.
+    Per head: dt = softplus(dt_raw + dt_bias), S = exp(-exp(a_log) dt) S + dt B x^T,
+    y = S^T C + d_skip x.  Returns fp32 [T, heads * vdim]."""
+    for name, t in (("dt_bias", dt_bias), ("a_log", a_log), ("d_skip", d_skip),
+                    ("state", state)):
+        _chk(name, t, torch.float32)
+    width = heads * vdim + 2 * groups * nstate
+    ld = _row_view("ssd_recurrence: xbc", xbc, width)
+    ld_dt = _row_view("ssd_recurrence: dt", dt_raw, heads)
+    T = xbc.shape[0]
+    if dt_raw.dtype != xbc.dtype or dt_raw.shape[0] != T or \
+            tuple(state.shape[1:]) != (heads, nstate, vdim) or \
+            not (dt_bias.numel() == a_log.numel() == d_skip.numel() == heads):
+        raise KernelError("ssd_recurrence: inputs and state do not fit together")
+    out = torch.empty((T, heads * vdim), dtype=torch.float32, device=xbc.device)
+    _check(_lib().ix_ssd_recurrence(
+        _ptr(xbc), ctypes.c_longlong(ld), _ptr(dt_raw), ctypes.c_longlong(ld_dt),
+        _dtype_code(xbc), _ptr(dt_bias), _ptr(a_log), _ptr(d_skip), _ptr(state), _ptr(step.cu_q),
+        _ptr(step.state_slot), _ptr(out), step.num_seqs, heads, vdim, nstate, groups, _stream()),
+        "ssd_recurrence")
+    _count()
+    return out
+
+
+def delta_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta_raw: torch.Tensor,
+                     decay: torch.Tensor, state: torch.Tensor, step, heads: int, kv_heads: int,
+                     dim: int, vdim: int, unit_eps: float, q_scale: float):
+    """Gated delta rule.  q, k [T, kv_heads * dim], v [T, heads * vdim], ``beta_raw``
+    [T, heads] are views with unit inner stride; ``decay`` fp32 [T, heads * dim]; ``state``
+    fp32 [slots, heads, dim, vdim], updated.  q and k become unit vectors per head
+    (x / sqrt(sum x^2 + unit_eps)), q also times ``q_scale``; beta = sigmoid(beta_raw).
+    Per head: S = diag(g) S; u = beta (v - S^T k); S += k u^T; o = S^T q.  Returns fp32
+    [T, heads, vdim]."""
+    ldq = _row_view("delta_recurrence: q", q, kv_heads * dim)
+    ldk = _row_view("delta_recurrence: k", k, kv_heads * dim)
+    ldv = _row_view("delta_recurrence: v", v, heads * vdim)
+    ldb = _row_view("delta_recurrence: beta", beta_raw, heads)
+    _chk("decay", decay, torch.float32)
+    _chk("state", state, torch.float32)
+    T = q.shape[0]
+    if not (q.dtype == k.dtype == v.dtype == beta_raw.dtype) or \
+            decay.shape != (T, heads * dim) or tuple(state.shape[1:]) != (heads, dim, vdim):
+        raise KernelError("delta_recurrence: inputs and state do not fit together")
+    out = torch.empty((T, heads, vdim), dtype=torch.float32, device=q.device)
+    _check(_lib().ix_delta_recurrence(
+        _ptr(q), ctypes.c_longlong(ldq), _ptr(k), ctypes.c_longlong(ldk), _ptr(v),
+        ctypes.c_longlong(ldv), _ptr(beta_raw), ctypes.c_longlong(ldb), _dtype_code(q),
+        _ptr(decay), _ptr(state), _ptr(step.cu_q), _ptr(step.state_slot), _ptr(out),
+        step.num_seqs, heads, kv_heads, dim, vdim, ctypes.c_float(unit_eps),
+        ctypes.c_float(q_scale), _stream()), "delta_recurrence")
+    _count()
+    return out
+
+
+def gated_group_norm(y: torch.Tensor, z: torch.Tensor, gain: torch.Tensor, groups: int,
+                     eps: float):
+    """groupnorm(y * silu(z)) * gain: y fp32 [T, W], z [T, W] a view in the run's element
+    type; the row is RMS-normed in ``groups`` equal parts.  Returns [T, W] in z's type."""
+    _chk("y", y, torch.float32)
+    _chk("gain", gain, torch.float32)
+    T, W = y.shape
+    ldz = _row_view("gated_group_norm: z", z, W)
+    if gain.numel() != W or z.shape[0] != T or groups <= 0 or W % groups:
+        raise KernelError("gated_group_norm: gain, gate or groups do not fit the rows")
+    out = torch.empty((T, W), dtype=z.dtype, device=y.device)
+    _check(_lib().ix_gated_group_norm(_ptr(y), _ptr(z), _dtype_code(z), ctypes.c_longlong(ldz),
+                                      _ptr(gain), _ptr(out), T, W, groups, ctypes.c_float(eps),
+                                      _stream()), "gated_group_norm")
+    _count()
+    return out
+
+
+def normed_pair_mean(left: torch.Tensor, right: torch.Tensor, gain_left: torch.Tensor,
+                     gain_right: torch.Tensor, eps: float):
+    """fp32 [T, W]: (left / rms(left) * gain_left + right / rms(right) * gain_right) / 2."""
+    _chk("left", left)
+    _chk("right", right, left.dtype)
+    _chk("gain_left", gain_left, torch.float32)
+    _chk("gain_right", gain_right, torch.float32)
+    T, W = left.shape
+    if right.shape != left.shape or gain_left.numel() != W or gain_right.numel() != W:
+        raise KernelError("normed_pair_mean: shapes differ")
+    out = torch.empty((T, W), dtype=torch.float32, device=left.device)
+    _check(_lib().ix_normed_pair_mean(_ptr(left), _ptr(right), _dtype_code(left), _ptr(gain_left),
+                                      _ptr(gain_right), _ptr(out), T, W, ctypes.c_float(eps),
+                                      _stream()), "normed_pair_mean")
+    _count()
+    return out
+
+
+def relu_squared(x: torch.Tensor):
+    """max(x, 0)^2 in x's element type."""
+    _chk("x", x)
+    out = torch.empty_like(x)
+    _check(_lib().ix_relu_squared(_ptr(x), _ptr(out), _dtype_code(x),
+                                  ctypes.c_longlong(x.numel()), _stream()), "relu_squared")
+    _count()
+    return out
+
+
+def table_route(token_ids: torch.Tensor, table: torch.Tensor, num_experts: int):
+    """(weights fp32 [T, top], experts int32 [T, top]): row ``token id`` of ``table``
+    int32 [vocab, top]; every weight is 1 / top."""
+    _chk("token_ids", token_ids, torch.int32)
+    _chk("table", table, torch.int32)
+    T = token_ids.numel()
+    vocab, top = table.shape
+    idx = torch.empty((T, top), dtype=torch.int32, device=table.device)
+    wts = torch.empty((T, top), dtype=torch.float32, device=table.device)
+    _check(_lib().ix_table_route(_ptr(token_ids), _ptr(table), _ptr(idx), _ptr(wts), T, top,
+                                 vocab, num_experts, _stream()), "table_route")
+    _count()
+    return wts, idx
+
+
+def scale_rows(x: torch.Tensor, scale: float):
+    """x *= scale in place (fp32)."""
+    _chk("x", x, torch.float32)
+    _check(_lib().ix_scale_rows(_ptr(x), ctypes.c_float(scale), ctypes.c_longlong(x.numel()),
+                                _stream()), "scale_rows")
+    _count()
+    return x
+
+
+def check_delta_limits(dim: int, taps: int, where: str = ""):
+    most = _lib().ix_delta_recurrence_max_dim()
+    if dim > most:
+        raise KernelError(f"{where}: {dim} state entries per column exceed the recurrence "
+                          f"kernels' {most}")
+    if not 1 <= taps <= 16:
+        raise KernelError(f"{where}: a convolution of {taps} taps is not one the kernel takes "
+                          "(1 to 16)")

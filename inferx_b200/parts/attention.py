@@ -16,11 +16,21 @@ from .base import PagedKvNeed
 from .registry import build_part, register_part
 
 
+_HF_NAMES = ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight",
+             "q_proj.bias", "k_proj.bias", "v_proj.bias")
+
+
 class AttentionMixer:
+    """Grouped-query attention.  The value heads may have a size of their own
+    (``spec.value_dim``): the value pages are then that wide and the fp32-arithmetic
+    kernels run; they also run when the spec asks for 32-bit softmax weights."""
+
     def __init__(self, spec, ctx, prefix: str):
         self.spec = spec
         self.ctx = ctx
         self.prefix = prefix
+        self.vdim = int(getattr(spec, "value_dim", 0) or spec.head_dim)
+        self.exact = bool(getattr(spec, "fp32_weights", False))
         self.position = build_part("position", spec.position, ctx, prefix)
         self.qkv_w = self.qkv_b = self.o_w = None
 
@@ -28,44 +38,60 @@ class AttentionMixer:
         check = getattr(self.ctx.ops, "check_attention_limits", None)
         if check is not None:
             s = self.spec
-            check(s.heads, s.kv_heads, s.head_dim, self.ctx.dtype, self.prefix)
+            check(s.heads, s.kv_heads, s.head_dim, self.ctx.dtype, self.prefix,
+                  allow_odd=self.exact or self.vdim != s.head_dim)
+            if self.vdim != s.head_dim:
+                check(s.heads, s.kv_heads, self.vdim, self.ctx.dtype, self.prefix, allow_odd=True)
+
+    def _names(self):
+        names = tuple(getattr(self.spec, "names", _HF_NAMES))
+        return [f"{self.prefix}.{n}" for n in names + _HF_NAMES[len(names):]]
 
     # -- weights -----------------------------------------------------------
     def tensors(self):
-        s, p = self.spec, self.prefix
-        dq, dkv = s.heads * s.head_dim, s.kv_heads * s.head_dim
+        s = self.spec
+        q, k, v, o, qb, kb, vb = self._names()
+        dq, dk, dv = s.heads * s.head_dim, s.kv_heads * s.head_dim, s.kv_heads * self.vdim
         decls = [
-            TensorDecl(f"{p}.q_proj.weight", (dq, s.hidden)),
-            TensorDecl(f"{p}.k_proj.weight", (dkv, s.hidden)),
-            TensorDecl(f"{p}.v_proj.weight", (dkv, s.hidden)),
-            TensorDecl(f"{p}.o_proj.weight", (s.hidden, dq)),
+            TensorDecl(q, (dq, s.hidden)),
+            TensorDecl(k, (dk, s.hidden)),
+            TensorDecl(v, (dv, s.hidden)),
+            TensorDecl(o, (s.hidden, s.heads * self.vdim)),
         ]
         if s.qkv_bias:
             decls += [
-                TensorDecl(f"{p}.q_proj.bias", (dq,), keep="float32", init="bias"),
-                TensorDecl(f"{p}.k_proj.bias", (dkv,), keep="float32", init="bias"),
-                TensorDecl(f"{p}.v_proj.bias", (dkv,), keep="float32", init="bias"),
+                TensorDecl(qb, (dq,), keep="float32", init="bias"),
+                TensorDecl(kb, (dk,), keep="float32", init="bias"),
+                TensorDecl(vb, (dv,), keep="float32", init="bias"),
             ]
         if self.position is not None:
             decls += self.position.tensors()
         return decls
 
     def bind(self, w):
-        p = self.prefix
-        self.qkv_w = torch.cat([w[f"{p}.q_proj.weight"], w[f"{p}.k_proj.weight"],
-                                w[f"{p}.v_proj.weight"]], dim=0).contiguous()
-        self.o_w = w[f"{p}.o_proj.weight"]
+        q, k, v, o, qb, kb, vb = self._names()
+        self.qkv_w = torch.cat([w[q], w[k], w[v]], dim=0).contiguous()
+        self.o_w = w[o]
         if self.spec.qkv_bias:
-            self.qkv_b = torch.cat([w[f"{p}.q_proj.bias"], w[f"{p}.k_proj.bias"],
-                                    w[f"{p}.v_proj.bias"]], dim=0).contiguous()
+            self.qkv_b = torch.cat([w[qb], w[kb], w[vb]], dim=0).contiguous()
         if self.position is not None:
             self.position.bind(w)
 
     # -- cache -------------------------------------------------------------
     def cache_needs(self):
-        return [PagedKvNeed(self.spec.kv_heads, self.spec.head_dim, self.spec.window)]
+        s = self.spec
+        if self.vdim != s.head_dim:
+            return [PagedKvNeed(s.kv_heads, s.head_dim, s.window,
+                                entry_dims=(s.head_dim, self.vdim))]
+        return [PagedKvNeed(s.kv_heads, s.head_dim, s.window)]
 
     # -- step --------------------------------------------------------------
+    def _project_out(self, attn, tokens):
+        s = self.spec
+        out_dtype = torch.float32 if getattr(s, "out_float32", False) else None
+        return self.ctx.ops.linear(attn.view(tokens, s.heads * self.vdim), self.o_w,
+                                   out_dtype=out_dtype)
+
     def forward(self, x, step, cache):
         s, ops = self.spec, self.ctx.ops
         group = step.groups[cache.group]
@@ -73,6 +99,19 @@ class AttentionMixer:
         if self.position is not None:
             inv_freq, rot = self.position.rotary_table()
         custom = getattr(self.position, "apply", None)
+        plain = self.vdim == s.head_dim and not self.exact
+        if not plain:
+            if custom is not None:
+                raise ValueError(f"{self.prefix}: a position encoding that is not a rotation "
+                                 "table is not combined with value heads of another size")
+            qkv = ops.linear(x, self.qkv_w)
+            q = ops.qkv_rope_append(
+                qkv, self.qkv_b, step.positions, inv_freq, rot, s.heads, s.kv_heads, s.head_dim,
+                cache.k if cache.writes else None, cache.v if cache.writes else None,
+                group.slots if cache.writes else None, value_dim=self.vdim)
+            attn = ops.paged_attention(q, cache.k, cache.v, group.block_table, step, s.window,
+                                       s.scale, fp32_weights=True)
+            return self._project_out(attn, step.num_tokens)
         fused = getattr(ops, "qkv_project_applies", None)
         if custom is None and cache.writes and fused is not None and fused(
                 x, self.qkv_w, s.heads, s.kv_heads, s.head_dim, rot):
@@ -82,7 +121,7 @@ class AttentionMixer:
                 s.head_dim, cache.k, cache.v, group.slots)
             attn = ops.paged_attention(q, cache.k, cache.v, group.block_table, step, s.window,
                                        s.scale)
-            return ops.linear(attn.view(step.num_tokens, s.heads * s.head_dim), self.o_w)
+            return self._project_out(attn, step.num_tokens)
         qkv = ops.linear(x, self.qkv_w)
         if custom is None:
             q = ops.qkv_rope_append(
@@ -98,7 +137,7 @@ class AttentionMixer:
             if cache.writes:
                 ops.append_kv(k, v, cache.k, cache.v, group.slots)
         attn = ops.paged_attention(q, cache.k, cache.v, group.block_table, step, s.window, s.scale)
-        return ops.linear(attn.view(step.num_tokens, s.heads * s.head_dim), self.o_w)
+        return self._project_out(attn, step.num_tokens)
 
 
 register_part("mixer", "attention", AttentionMixer)

@@ -56,10 +56,15 @@ class PagedKvNeed:
     window: int = 0
     entries: Tuple[str, ...] = ("k", "v")
     dtype: Optional[torch.dtype] = None
+    # a head size per entry where they differ (values wider than keys, say); None: head_dim
+    entry_dims: Optional[Tuple[int, ...]] = None
+
+    def dim_of(self, index: int) -> int:
+        return self.head_dim if self.entry_dims is None else int(self.entry_dims[index])
 
     def bytes_per_token(self, run_dtype: torch.dtype) -> int:
         esize = torch.empty((), dtype=self.dtype or run_dtype).element_size()
-        return len(self.entries) * self.kv_heads * self.head_dim * esize
+        return sum(self.kv_heads * self.dim_of(i) * esize for i in range(len(self.entries)))
 
 
 @dataclass(frozen=True)
@@ -123,12 +128,14 @@ class StepContext:
 @dataclass
 class PendingSum:
     """Contributions to the residual stream that have not been added yet: tensors
-    [T, width] (fp32 or the run's element type) and at most one fp32 vector [width]
-    added to every row.  A norm that knows this class adds them in the pass in which it
-    normalises; anything else calls ``materialize`` and adds the one tensor it gets."""
+    [T, width] (fp32 or the run's element type), whose sum is multiplied by ``scale``, and
+    at most one fp32 vector [width] added to every row (not scaled).  A norm that knows
+    this class adds them in the pass in which it normalises; anything else calls
+    ``materialize`` and adds the one tensor it gets."""
     terms: List[Any] = field(default_factory=list)
     vector: Optional[torch.Tensor] = None
     dtype: Optional[torch.dtype] = None       # what ``materialize`` returns
+    scale: float = 1.0
 
     def materialize(self) -> torch.Tensor:
         total = None
@@ -136,6 +143,8 @@ class PendingSum:
             if hasattr(t, "materialize"):
                 t = t.materialize()
             total = t.to(torch.float32) if total is None else total + t.to(torch.float32)
+        if total is not None and self.scale != 1.0:
+            total = total * self.scale
         if self.vector is not None:
             total = self.vector.to(torch.float32) if total is None else total + self.vector
         return total.to(self.dtype or torch.float32)

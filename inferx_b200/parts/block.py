@@ -23,21 +23,35 @@ from .registry import build_part, register_part
 
 
 class PreNormBlock:
-    """``x += mixer(norm(x)); x += ffn(norm(x))`` on the fp32 residual stream."""
+    """``x += m * mixer(norm(x)); x += m * ffn(norm(x))`` on the fp32 residual stream, with
+    ``m`` the spec's ``residual_scale`` (1 unless the design scales its sublayers); a layer
+    may have no feed-forward."""
 
     def __init__(self, spec, ctx: BuildContext, prefix: str):
         p = prefix
-        self.spec = spec
+        self.spec, self.ctx = spec, ctx
+        self.scale = float(getattr(spec, "residual_scale", 1.0))
         self.input_norm = build_part("norm", spec.input_norm, ctx, f"{p}.{spec.input_norm_name}")
         self.mixer = build_part("mixer", spec.mixer, ctx, f"{p}.{spec.mixer_name}")
-        self.post_norm = build_part("norm", spec.post_norm, ctx, f"{p}.{spec.post_norm_name}")
         self.ffn = build_part("feed_forward", spec.ffn, ctx, f"{p}.{spec.ffn_name}")
+        self.post_norm = (build_part("norm", spec.post_norm, ctx, f"{p}.{spec.post_norm_name}")
+                          if self.ffn is not None else None)
 
     def parts(self):
-        return [self.input_norm, self.mixer, self.post_norm, self.ffn]
+        return [x for x in (self.input_norm, self.mixer, self.post_norm, self.ffn)
+                if x is not None]
 
     def cache_needs(self):
         return list(self.mixer.cache_needs())
+
+    def _scaled(self, term, norm):
+        """A sublayer's output as the next norm takes it: times the residual scale."""
+        if self.scale == 1.0:
+            return term
+        pending = PendingSum(terms=[term], dtype=self.ctx.dtype, scale=self.scale)
+        if norm is None or getattr(norm, "accepts_scaled", False):
+            return pending
+        return pending.materialize()
 
     def forward(self, resid, pending, step: StepContext, cache: LayerCache):
         """``pending`` is the previous block's contribution not yet added to
@@ -47,8 +61,10 @@ class PreNormBlock:
             pending = pending.materialize()
         n = self.input_norm.forward(resid, pending)
         a = self.mixer.forward(n, step, cache)
-        n = self.post_norm.forward(resid, a)
-        return self.ffn.forward(n, step)
+        if self.ffn is None:
+            return self._scaled(a, None)
+        n = self.post_norm.forward(resid, self._scaled(a, self.post_norm))
+        return self._scaled(self.ffn.forward(n, step), None)
 
 
 class SublayerNormBlock:
@@ -164,8 +180,10 @@ class DecoderModel:
                         if getattr(e, "cache_copy", 0)})
         self.cache_units = [(i, 0) for i in range(len(self.blocks))] + extra
         self._unit_index = {u: i for i, u in enumerate(self.cache_units)}
-        self._keeps_embedding = any(getattr(e, "before", None) is not None and e.before.embedding
-                                    for e in spec.schedule)
+        self._keeps_embedding = any(
+            getattr(e, "before", None) is not None
+            and (e.before.embedding or getattr(e.before, "project", None))
+            for e in spec.schedule)
         if ctx.ops is not None:
             # sizes beyond what the kernels take are refused now, not at the first launch
             for b in self.blocks:
@@ -187,6 +205,10 @@ class DecoderModel:
                     raise ValueError(f"table {b.table!r} is given two sizes in the schedule")
         decls += [TensorDecl(name, (rows, s.hidden), keep="float32", init="bias")
                   for name, rows in tables.items()]
+        projections = sorted({e.before.project for e in s.schedule
+                              if getattr(e, "before", None) is not None
+                              and getattr(e.before, "project", None)})
+        decls += [TensorDecl(name, (s.hidden, 2 * s.hidden)) for name in projections]
         return decls
 
     def tensors(self) -> List[TensorDecl]:
@@ -210,6 +232,7 @@ class DecoderModel:
         self.head = self.embed if self.spec.tied_head else own[self.spec.head_name]
         self.stream_tables = {n: t for n, t in own.items()
                               if n not in (self.spec.embed_name, self.spec.head_name)}
+        # (the matrices of stream projections live in the same table, by name)
         for b in self.blocks:
             for part in b.parts():
                 part.bind(fetch(part.tensors()))
@@ -225,18 +248,42 @@ class DecoderModel:
         """The cache unit a schedule entry reads and writes."""
         return self._unit_index[(entry.cache_layer, getattr(entry, "cache_copy", 0))]
 
+    def _project_stream(self, resid, pending, before, embedded):
+        """The stream becomes W [x; x0]: what is pending is added while the two halves are
+        laid side by side in the run's element type, and the product leaves in fp32."""
+        ops = self.ctx.ops
+        scale, vector, delta = 1.0, None, pending
+        if hasattr(pending, "terms"):
+            scale, vector = float(getattr(pending, "scale", 1.0)), pending.vector
+            if len(pending.terms) == 1:
+                delta = pending.terms[0]
+            elif not pending.terms:
+                delta = None
+            else:
+                delta, scale = PendingSum(terms=pending.terms, dtype=torch.float32,
+                                          scale=scale).materialize(), 1.0
+        both = ops.stream_concat(resid, delta, scale, vector, embedded, self.ctx.dtype)
+        return ops.linear(both, self.stream_tables[before.project], out_dtype=torch.float32)
+
     def _add_before(self, pending, before, embedded):
         """What a run's ``before`` names joins what is still to be added to the stream."""
-        terms = []
+        terms, scale, vector = [], 1.0, None
         if pending is not None:
-            terms = list(pending.terms) if hasattr(pending, "terms") else [pending]
-        vector = getattr(pending, "vector", None)
+            if hasattr(pending, "terms"):
+                scale = float(getattr(pending, "scale", 1.0))
+                if scale != 1.0 and before.embedding:
+                    # the embedding output joins unscaled: the scaled sum is written first
+                    terms, scale = [pending.materialize()], 1.0
+                else:
+                    terms, vector = list(pending.terms), pending.vector
+            else:
+                terms = [pending]
         if before.embedding:
             terms.append(embedded)
         if before.table is not None:
             row = self.stream_tables[before.table][before.row]
             vector = row if vector is None else vector + row
-        return PendingSum(terms=terms, vector=vector, dtype=self.ctx.dtype)
+        return PendingSum(terms=terms, vector=vector, dtype=self.ctx.dtype, scale=scale)
 
     # -- step --------------------------------------------------------------
     def forward(self, step: StepContext, caches: List[LayerCache],
@@ -257,6 +304,9 @@ class DecoderModel:
         pending = None
         for entry, cache in zip(self.spec.schedule, caches):
             if getattr(entry, "before", None) is not None:
+                if getattr(entry.before, "project", None):
+                    resid = self._project_stream(resid, pending, entry.before, embedded)
+                    pending = None
                 pending = self._add_before(pending, entry.before, embedded)
             pending = self.blocks[entry.layer].forward(resid, pending, step, cache)
         if logit_rows is None or logit_rows.numel() == 0:
@@ -265,7 +315,9 @@ class DecoderModel:
                                                             False):
             pending = pending.materialize()
         n = self.final_norm.forward(resid, pending, rows=logit_rows)
-        return ops.linear(n, self.head, out_dtype=torch.float32)
+        logits = ops.linear(n, self.head, out_dtype=torch.float32)
+        scale = float(getattr(self.spec, "logit_scale", 1.0))
+        return logits if scale == 1.0 else ops.scale_rows(logits, scale)
 
 
 Block = PreNormBlock

@@ -241,6 +241,92 @@ class MoeFeedForward:
         return combine(y, dest, topk_w, shared, shared_logit)
 
 
+class ReluSquaredFeedForward:
+    """``down(relu(up h)^2)``, no biases; the result leaves in fp32 for the norm that adds
+    it."""
+
+    def __init__(self, spec, ctx, prefix: str):
+        self.spec, self.ctx, self.prefix = spec, ctx, prefix
+        self.up_w = self.down_w = None
+
+    def tensors(self):
+        s, p = self.spec, self.prefix
+        u, d = s.names
+        return [TensorDecl(f"{p}.{u}", (s.intermediate, s.hidden)),
+                TensorDecl(f"{p}.{d}", (s.hidden, s.intermediate))]
+
+    def bind(self, w):
+        u, d = self.spec.names
+        self.up_w, self.down_w = w[f"{self.prefix}.{u}"], w[f"{self.prefix}.{d}"]
+
+    def forward(self, x, step=None):
+        ops = self.ctx.ops
+        act = ops.relu_squared(ops.linear(x, self.up_w))
+        return ops.linear(act, self.down_w, out_dtype=torch.float32)
+
+
+class TableMoeFeedForward:
+    """Mixture of gated experts whose choice is a table look-up: row ``token id`` of an
+    integer table [vocab, top] names the token's experts, each with weight 1 / top.  After
+    the look-up it is the routed mixture's own path: stable dispatch by expert, grouped
+    gate/up product with silu(gate) * up, grouped down product, combine in slot order with
+    fp32 weights."""
+
+    def __init__(self, spec, ctx, prefix: str):
+        self.spec, self.ctx, self.prefix = spec, ctx, prefix
+        if not 0 < spec.top_k <= spec.num_experts:
+            raise ValueError(f"{prefix}: {spec.top_k} of {spec.num_experts} experts")
+        self.table = self.expert_gate_up = self.expert_down = None
+
+    def check_limits(self):
+        check = getattr(self.ctx.ops, "check_router_limits", None)
+        if check is not None:
+            check(self.spec.hidden, self.spec.num_experts, self.spec.top_k, self.prefix)
+
+    def _expert_names(self, e: int):
+        return tuple(f"{self.prefix}.{n.format(e=e)}" for n in self.spec.expert_names)
+
+    def tensors(self):
+        s, p = self.spec, self.prefix
+        decls = [TensorDecl(f"{p}.{s.table_name}", (s.vocab, s.top_k), keep="int32",
+                            init="distinct", high=s.num_experts)]
+        for e in range(s.num_experts):
+            g, u, d = self._expert_names(e)
+            decls += [TensorDecl(g, (s.expert_intermediate, s.hidden)),
+                      TensorDecl(u, (s.expert_intermediate, s.hidden)),
+                      TensorDecl(d, (s.hidden, s.expert_intermediate))]
+        return decls
+
+    def bind(self, w):
+        s, p = self.spec, self.prefix
+        self.table = w[f"{p}.{s.table_name}"].contiguous()
+        lo, hi = int(self.table.min()), int(self.table.max())
+        if lo < 0 or hi >= s.num_experts:
+            raise ValueError(f"{p}.{s.table_name}: entries {lo}..{hi} name experts outside "
+                             f"0..{s.num_experts - 1}")
+        gu = torch.empty((s.num_experts, 2 * s.expert_intermediate, s.hidden),
+                         dtype=self.ctx.dtype, device=self.ctx.device)
+        dn = torch.empty((s.num_experts, s.hidden, s.expert_intermediate),
+                         dtype=self.ctx.dtype, device=self.ctx.device)
+        for e in range(s.num_experts):
+            g, u, d = self._expert_names(e)
+            gu[e, :s.expert_intermediate] = w[g]
+            gu[e, s.expert_intermediate:] = w[u]
+            dn[e] = w[d]
+        self.expert_gate_up, self.expert_down = gu, dn
+
+    def forward(self, x, step=None):
+        s, ops = self.spec, self.ctx.ops
+        topk_w, topk_idx = ops.table_route(step.token_ids, self.table, s.num_experts)
+        offsets, rows, dest = ops.moe_dispatch(topk_idx, s.num_experts)
+        act = ops.grouped_gate_up_swiglu(x, rows, offsets, self.expert_gate_up)
+        y = ops.grouped_down(act, offsets, self.expert_down, offsets_settled=True)
+        combine = getattr(ops, "moe_combine_pending", ops.moe_combine)
+        return combine(y, dest, topk_w, None, None)
+
+
 register_part("feed_forward", "swiglu", SwiGluFeedForward)
 register_part("feed_forward", "moe", MoeFeedForward)
 register_part("feed_forward", "clamped_glu", ClampedGluFeedForward)
+register_part("feed_forward", "relu_squared", ReluSquaredFeedForward)
+register_part("feed_forward", "moe_table", TableMoeFeedForward)

@@ -10,6 +10,8 @@ pass, on an fp32 residual stream.
 """
 from __future__ import annotations
 
+import torch
+
 from ..weights.loader import TensorDecl
 from .registry import register_part
 
@@ -53,6 +55,43 @@ class RmsNorm:
 
 
 register_part("norm", "rmsnorm", RmsNorm)
+
+
+class LayerNorm:
+    """(x - mean) / sqrt(mean((x - mean)^2) + eps) * gain, no bias, all in fp32, with the
+    residual add folded in: what is pending (one tensor times a scale, and a vector) is
+    added to the stream in the pass that normalises it."""
+    accepts_pending = True
+    accepts_scaled = True
+
+    def __init__(self, spec, ctx, prefix: str):
+        self.spec, self.ctx = spec, ctx
+        self.name = f"{prefix}{getattr(spec, 'suffix', '.weight')}"
+        self.gain = None
+
+    def tensors(self):
+        return [TensorDecl(self.name, (self.spec.size,), keep="float32", init="gain")]
+
+    def bind(self, weights):
+        self.gain = weights[self.name]
+
+    def forward(self, resid, delta, rows=None):
+        scale, vector = 1.0, None
+        if hasattr(delta, "terms"):
+            scale, vector = float(getattr(delta, "scale", 1.0)), delta.vector
+            if len(delta.terms) == 1:
+                delta = delta.terms[0]
+            elif not delta.terms:
+                delta = None
+            else:                       # several tensors: their scaled sum, written once
+                vector_free = type(delta)(terms=delta.terms, dtype=torch.float32,
+                                          scale=delta.scale)
+                delta, scale = vector_free.materialize(), 1.0
+        return self.ctx.ops.add_scaled_norm(resid, delta, scale, vector, self.gain,
+                                            self.spec.eps, self.ctx.dtype, center=True, rows=rows)
+
+
+register_part("norm", "layernorm", LayerNorm)
 
 
 class GroupedRmsNorm:

@@ -24,7 +24,12 @@ class RotaryEncoding:
         half = spec.rotary_dim // 2
         j = torch.arange(half, dtype=torch.float64)
         inv = torch.pow(torch.tensor(float(spec.theta), dtype=torch.float64),
-                        -2.0 * j / float(spec.rotary_dim))
+                        -2.0 * j / float(max(spec.rotary_dim, 1)))
+        factor = float(getattr(spec, "scaling_factor", 1.0))
+        if factor <= 0:
+            raise ValueError(f"rotary scaling factor {factor} must be positive")
+        if factor != 1.0:
+            inv = inv / factor        # linear position scaling, in float64 before the rounding
         self.inv_freq = inv.to(torch.float32).to(ctx.device)
 
     def tensors(self):

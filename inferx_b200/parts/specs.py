@@ -39,11 +39,23 @@ class SinusoidSpec:
 
 
 @dataclass(frozen=True)
+class LayerNormSpec:
+    """(x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps) * w: a layer norm with a gain and
+    no bias.  ``suffix`` is what the tensor's name adds to the part's prefix."""
+    size: int
+    eps: float
+    suffix: str = ".weight"
+    kind: str = "layernorm"
+
+
+@dataclass(frozen=True)
 class RopeSpec:
-    """Half-split (NeoX) rotary encoding of the first ``rotary_dim`` of each head."""
+    """Half-split (NeoX) rotary encoding of the first ``rotary_dim`` of each head.  Every
+    frequency is divided by ``scaling_factor`` (linear position scaling; 1: none)."""
     head_dim: int
     rotary_dim: int
     theta: float
+    scaling_factor: float = 1.0
     kind: str = "rope"
 
 
@@ -123,6 +135,12 @@ class ClampedGluSpec:
 
 @dataclass(frozen=True)
 class AttentionSpec:
+    """Grouped-query softmax attention.  ``value_dim`` is the size of a value head when it
+    differs from the query/key size ``head_dim`` (0: the same).  ``fp32_weights``: scores,
+    softmax weights and their products with the values stay in 32-bit arithmetic whatever
+    the element type (the tensor-core kernels round the weights to the values' type).
+    ``names`` are the tensors of q, k, v, o (and their biases) inside the prefix;
+    ``out_float32``: the output projection leaves in fp32."""
     hidden: int
     heads: int
     kv_heads: int
@@ -131,6 +149,11 @@ class AttentionSpec:
     scale: float
     window: int  # keys visible to a query including itself; 0 = all
     position: Any  # a position-encoding spec, or None
+    value_dim: int = 0
+    fp32_weights: bool = False
+    out_float32: bool = False
+    names: tuple = ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight",
+                    "q_proj.bias", "k_proj.bias", "v_proj.bias")
     kind: str = "attention"
 
 
@@ -191,6 +214,93 @@ class WkvSpec:
 
 
 @dataclass(frozen=True)
+class StateSpaceSpec:
+    """Selective state space with a scalar decay per head (state-space duality): one input
+    projection laid out [z: inner | x: inner | B: groups * state | C: groups * state | dt:
+    heads] with inner = heads * vdim; x, B and C pass a causal convolution of ``conv`` taps
+    per channel (with bias) and silu; dt = softplus(dt + dt_bias);
+    S_t = exp(-exp(A_log) dt) S_(t-1) + dt B_t x_t^T, y_t = S_t^T C_t + D x_t per head (head
+    h reads group h // (heads / groups)); y * silu(z) is RMS-normed in ``norm_groups`` equal
+    parts, multiplied by a gain and projected.  State per request: S [heads, state, vdim]
+    fp32 and the last conv - 1 inputs of the convolution."""
+    hidden: int
+    heads: int
+    vdim: int
+    state: int
+    groups: int
+    conv: int
+    norm_groups: int
+    norm_eps: float
+    names: tuple = (("in", "in"), ("conv", "conv"), ("conv_bias", "conv.b"),
+                    ("dt_bias", "dt_bias"), ("a_log", "A_log"), ("d", "D"), ("norm", "norm"),
+                    ("o", "o"))
+    kind: str = "state_space"
+
+
+@dataclass(frozen=True)
+class GatedDeltaSpec:
+    """Delta rule with a decay per head and key channel.  q, k ([kv_heads, dim]) and v
+    ([heads, vdim]) each pass a causal convolution of ``conv`` taps per channel (no bias)
+    and silu; q and k become unit vectors per head (x / sqrt(sum x^2 + unit_eps)), q times
+    dim^(-1/2); beta = sigmoid(W_b h); decay g = exp(-exp(A_log_h) softplus(W_a2 (W_a1 h) +
+    dt_bias)) [heads, dim].  Per head: S <- g * S; u = beta (v - S^T k); S <- S + k u^T;
+    o = S^T q.  o is RMS-normed per head (gain over vdim shared by the heads), multiplied by
+    sigmoid(W_g2 (W_g1 h)) and projected.  The inner sizes of the two low-rank products
+    are the checkpoint's when 0.  State per request: S [heads, dim, vdim] fp32 and the last
+    conv - 1 inputs of the convolutions."""
+    hidden: int
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    conv: int
+    norm_eps: float
+    unit_eps: float = 1e-6
+    decay_rank: int = 0
+    gate_rank: int = 0
+    kind: str = "gated_delta"
+
+
+@dataclass(frozen=True)
+class NormedPairSpec:
+    """Two mixers side by side reading the same input; the result is the mean of their
+    outputs, each first RMS-normed over the model width with a gain of its own
+    (``<name>.out`` inside the prefix)."""
+    hidden: int
+    left: Any
+    right: Any
+    norm_eps: float
+    left_name: str = "left"
+    right_name: str = "right"
+    gain_suffix: str = ".out"
+    kind: str = "normed_pair"
+
+
+@dataclass(frozen=True)
+class ReluSquaredSpec:
+    """down(relu(up h)^2), no biases."""
+    hidden: int
+    intermediate: int
+    names: tuple = ("up", "down")
+    kind: str = "relu_squared"
+
+
+@dataclass(frozen=True)
+class TableMoeSpec:
+    """Mixture of gated experts without a router: row ``token id`` of an integer table
+    [vocab, top] names the token's experts (the entries of a row differ); each has weight
+    1 / top.  Expert: down(silu(gate h) * (up h))."""
+    hidden: int
+    vocab: int
+    num_experts: int
+    top_k: int
+    expert_intermediate: int
+    table_name: str = "table"
+    expert_names: tuple = ("e{e}.gate", "e{e}.up", "e{e}.down")
+    kind: str = "moe_table"
+
+
+@dataclass(frozen=True)
 class SwiGluSpec:
     hidden: int
     intermediate: int
@@ -240,17 +350,22 @@ class LayerSpec:
     # a transform of what the mixer reads (a token shift, for instance), or None
     mixer_input: Any = None
     mixer_input_name: str = "shift"
+    # "pre_norm" only: each sublayer's output is multiplied by this before it is added
+    residual_scale: float = 1.0
 
 
 @dataclass(frozen=True)
 class StreamAddSpec:
-    """Something added to the residual stream ahead of a run: row ``row`` of the tensor
-    ``table`` ([rows, width], by its checkpoint name) and, with ``embedding``, the stream
-    as it was before the first run (the embedding output) once more."""
+    """Something done to the residual stream ahead of a run.  With ``project`` (a matrix
+    [width, 2 width] by its checkpoint name) the stream x first becomes W [x; x0], x0 being
+    the stream as it was before the first run (the embedding output).  Then row ``row`` of
+    the tensor ``table`` ([rows, width], by its checkpoint name) is added and, with
+    ``embedding``, the embedding output once more."""
     table: Optional[str] = None
     rows: int = 0
     row: int = 0
     embedding: bool = False
+    project: Optional[str] = None
 
 
 @dataclass(frozen=True)
@@ -289,4 +404,5 @@ class ModelSpec:
     final_norm_name: str = "model.norm"
     head_name: str = "lm_head.weight"
     embed_scale: float = 1.0     # the residual stream starts as embed[token] * embed_scale
+    logit_scale: float = 1.0     # the head's products are multiplied by this
     embed_position: Any = None   # a position spec whose vector is added to the embedding

@@ -50,6 +50,8 @@ class TensorDecl:
     shape: Tuple[int, ...]
     keep: str = "param"    # "param" (run dtype) | "float32" | "int32"
     init: str = "matrix"   # "matrix" N(0,std) | "gain" 1+N(0,std) | "bias" N(0,std) | "zeros"
+    # int32 tensors with init "distinct": every row holds distinct integers below ``high``
+    high: int = 0
 
 
 class WeightSource:
@@ -152,6 +154,21 @@ def counter_normal(key: int, numel: int, device, chunk: int = 0) -> torch.Tensor
     return out
 
 
+def counter_distinct_rows(key: int, shape, high: int, device) -> torch.Tensor:
+    """int32 [rows, n] with n <= high distinct integers below ``high`` in every row: row r
+    starts at a hash of (key, r) and counts upwards modulo ``high``."""
+    rows, n = (int(v) for v in shape)
+    if n > high:
+        raise WeightError(f"{n} distinct integers below {high} do not exist")
+    golden, m1, m2 = _i64(0x9E3779B97F4A7C15), _i64(0xBF58476D1CE4E5B9), _i64(0x94D049BB133111EB)
+    z = torch.arange(1, rows + 1, dtype=torch.int64, device=device) * golden + _i64(key)
+    z = (z ^ _lsr(z, 30)) * m1
+    z = (z ^ _lsr(z, 27)) * m2
+    start = _lsr(z ^ _lsr(z, 31), 33) % high
+    cols = torch.arange(n, dtype=torch.int64, device=device)
+    return ((start[:, None] + cols[None, :]) % high).to(torch.int32)
+
+
 class RandomSource(WeightSource):
     """Seeded weights: matrices and biases N(0, std), norm gains 1 + N(0, std).
 
@@ -173,6 +190,9 @@ class RandomSource(WeightSource):
 
     def fetch(self, decl):
         if decl.keep == "int32":
+            if decl.init == "distinct" and decl.high > 0:
+                return counter_distinct_rows(_name_seed(self.seed, decl.name), decl.shape,
+                                             decl.high, self.device)
             return torch.zeros(decl.shape, dtype=torch.int32, device=self.device)
         if decl.init == "zeros":
             return torch.zeros(decl.shape, dtype=torch.float32, device=self.device)

@@ -72,7 +72,7 @@ def _scatter(cache, rows, slots):
 
 
 def qkv_rope_append(qkv, bias, positions, inv_freq, rotary_dim, heads, kv_heads, head_dim,
-                    k_cache, v_cache, slots, want_dense_kv=False):
+                    k_cache, v_cache, slots, want_dense_kv=False, value_dim=0):
     T = qkv.shape[0]
     x = _f(qkv)
     if bias is not None:
@@ -80,7 +80,7 @@ def qkv_rope_append(qkv, bias, positions, inv_freq, rotary_dim, heads, kv_heads,
     dq, dkv = heads * head_dim, kv_heads * head_dim
     q = _rotate(x[:, :dq].reshape(T, heads, head_dim), positions, inv_freq, rotary_dim)
     k = _rotate(x[:, dq:dq + dkv].reshape(T, kv_heads, head_dim), positions, inv_freq, rotary_dim)
-    v = x[:, dq + dkv:].reshape(T, kv_heads, head_dim)
+    v = x[:, dq + dkv:].reshape(T, kv_heads, value_dim or head_dim)
     q, k, v = q.to(qkv.dtype), k.to(qkv.dtype), v.to(qkv.dtype)
     if k_cache is not None:
         _scatter(k_cache, k, slots)
@@ -98,7 +98,7 @@ def paged_attention_generic(q, k_cache, v_cache, block_table, seq_of_token, posi
     T, heads, hd = q.shape
     P, kvh, page, _ = k_cache.shape
     rep = heads // kvh
-    out = torch.zeros(T, heads, hd, dtype=torch.float32)
+    out = torch.zeros(T, heads, v_cache.shape[3], dtype=torch.float32)
     for t in range(T):
         s, pos = int(seq_of_token[t]), int(positions[t])
         start = max(0, pos - window + 1) if window > 0 else 0
@@ -118,7 +118,8 @@ def paged_attention_generic(q, k_cache, v_cache, block_table, seq_of_token, posi
     return out.to(q.dtype)
 
 
-def paged_attention(q, k_cache, v_cache, block_table, step, window, scale, softcap=0.0):
+def paged_attention(q, k_cache, v_cache, block_table, step, window, scale, softcap=0.0,
+                    fp32_weights=False):
     return paged_attention_generic(q, k_cache, v_cache, block_table, step.seq_of_token,
                                    step.positions, window, scale, softcap)
 
@@ -448,8 +449,12 @@ def shift_mix(x, mu, state, step):
     return out.to(x.dtype)
 
 
-def lowrank_decay(x, w2t, b, mode, tau=1.0):
+def lowrank_decay(x, w2t, b, mode, tau=1.0, head_log_rate=None):
     x = _f(x)
+    if mode == "exp_rate_softplus":
+        z = x @ w2t + (b if b is not None else 0.0)
+        rate = torch.exp(head_log_rate).repeat_interleave(w2t.shape[1] // head_log_rate.numel())
+        return torch.exp(-rate * torch.nn.functional.softplus(z, threshold=30.0))
     if mode == "exp_exp_tanh":
         return torch.exp(-torch.exp(torch.tanh(x) @ w2t + b))
     assert mode == "sigmoid_root"
@@ -478,9 +483,145 @@ def linear_recurrence(q, k, v, decay, bonus, state, step, heads, dim, vdim, q_sc
     return out
 
 
-def head_norm_gate(o, weight, gate, eps, out_dtype):
+def head_norm_gate(o, weight, gate, eps, out_dtype, gate_form="silu"):
     T, H, V = o.shape
     n = o / torch.sqrt((o * o).mean(-1, keepdim=True) + eps)
     n = n * (weight.reshape(H, V) if weight.numel() == H * V else weight)
     g = _f(gate).reshape(T, H, V)
-    return (n * (g / (1.0 + torch.exp(-g)))).reshape(T, H * V).to(out_dtype)
+    act = torch.sigmoid(g) if gate_form == "sigmoid" else g / (1.0 + torch.exp(-g))
+    return (n * act).reshape(T, H * V).to(out_dtype)
+
+
+# -- layers around a short convolution and a matrix of state; the scaled pre-norm ---------
+def _pending_total(resid, delta, delta_scale, vector):
+    if hasattr(delta, "materialize"):
+        delta = delta.materialize()
+    total = None
+    if delta is not None:
+        total = _f(delta) * delta_scale
+    if vector is not None:
+        total = vector[None, :].expand_as(resid) if total is None else total + vector
+    return total
+
+
+def add_scaled_norm(resid, delta, delta_scale, vector, gain, eps, out_dtype, center=True,
+                    rows=None):
+    total = _pending_total(resid, delta, delta_scale, vector)
+    if rows is None:
+        if total is not None:
+            resid += total
+        v = resid
+    else:
+        v = resid[rows.long()]
+        if total is not None:
+            v = v + total[rows.long()]
+    if center:
+        v = v - v.mean(-1, keepdim=True)
+    ms = (v * v).mean(-1, keepdim=True)
+    return (v / torch.sqrt(ms + eps) * gain).to(out_dtype)
+
+
+def stream_concat(resid, delta, delta_scale, vector, first, out_dtype):
+    total = _pending_total(resid, delta, delta_scale, vector)
+    x = resid if total is None else resid + total
+    return torch.cat([x, first], -1).to(out_dtype)
+
+
+def causal_conv(x, w, bias, state, step, silu=True):
+    T, C = x.shape
+    taps = w.shape[1]
+    out = torch.zeros(T, C)
+    for s in range(step.num_seqs):
+        a, b = int(step.cu_q[s]), int(step.cu_q[s + 1])
+        if b <= a:
+            continue
+        slot = int(step.state_slot[s])
+        past = state[slot] if taps > 1 else torch.zeros(0, C)
+        rows = torch.cat([past, _f(x[a:b])], 0)                   # [taps - 1 + n, C]
+        acc = torch.zeros(b - a, C) if bias is None else bias[None, :].repeat(b - a, 1)
+        for j in range(taps):
+            acc = acc + rows[j:j + b - a] * w[:, j]
+        out[a:b] = acc
+        if taps > 1:
+            state[slot] = rows[-(taps - 1):]
+    if silu:
+        out = out * torch.sigmoid(out)
+    return out.to(x.dtype)
+
+
+def ssd_recurrence(xbc, dt_raw, dt_bias, a_log, d_skip, state, step, heads, vdim, nstate,
+                   groups):
+    T = xbc.shape[0]
+    inner = heads * vdim
+    x = _f(xbc[:, :inner]).reshape(T, heads, vdim)
+    B = _f(xbc[:, inner:inner + groups * nstate]).reshape(T, groups, nstate)
+    C = _f(xbc[:, inner + groups * nstate:]).reshape(T, groups, nstate)
+    per = heads // groups
+    B, C = B.repeat_interleave(per, 1), C.repeat_interleave(per, 1)       # [T, heads, N]
+    dt = torch.nn.functional.softplus(_f(dt_raw) + dt_bias, threshold=30.0)
+    a = torch.exp(-torch.exp(a_log) * dt)
+    out = torch.zeros(T, heads, vdim)
+    for s in range(step.num_seqs):
+        slot = int(step.state_slot[s])
+        S = state[slot].clone()
+        for t in range(int(step.cu_q[s]), int(step.cu_q[s + 1])):
+            S = a[t][:, None, None] * S + (dt[t][:, None] * B[t])[:, :, None] * x[t][:, None, :]
+            out[t] = torch.einsum("hnv,hn->hv", S, C[t]) + d_skip[:, None] * x[t]
+        state[slot] = S
+    return out.reshape(T, inner)
+
+
+def delta_recurrence(q, k, v, beta_raw, decay, state, step, heads, kv_heads, dim, vdim,
+                     unit_eps, q_scale):
+    T = q.shape[0]
+    per = heads // kv_heads
+
+    def unit(z):
+        z = _f(z).reshape(T, kv_heads, dim)
+        return (z / torch.sqrt((z * z).sum(-1, keepdim=True) + unit_eps)).repeat_interleave(per, 1)
+
+    qf, kf = unit(q) * q_scale, unit(k)
+    vf = _f(v).reshape(T, heads, vdim)
+    beta = torch.sigmoid(_f(beta_raw))
+    g = decay.reshape(T, heads, dim)
+    out = torch.zeros(T, heads, vdim)
+    for s in range(step.num_seqs):
+        slot = int(step.state_slot[s])
+        S = state[slot].clone()
+        for t in range(int(step.cu_q[s]), int(step.cu_q[s + 1])):
+            S = g[t][:, :, None] * S
+            u = beta[t][:, None] * (vf[t] - torch.einsum("hkv,hk->hv", S, kf[t]))
+            S = S + kf[t][:, :, None] * u[:, None, :]
+            out[t] = torch.einsum("hkv,hk->hv", S, qf[t])
+        state[slot] = S
+    return out
+
+
+def gated_group_norm(y, z, gain, groups, eps):
+    T, W = y.shape
+    zz = _f(z)
+    v = (y * (zz * torch.sigmoid(zz))).reshape(T, groups, W // groups)
+    v = v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps)
+    return (v.reshape(T, W) * gain).to(z.dtype)
+
+
+def normed_pair_mean(left, right, gain_left, gain_right, eps):
+    def unit(v):
+        v = _f(v)
+        return v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps)
+    return 0.5 * (unit(left) * gain_left + unit(right) * gain_right)
+
+
+def relu_squared(x):
+    v = torch.relu(_f(x))
+    return (v * v).to(x.dtype)
+
+
+def table_route(token_ids, table, num_experts):
+    idx = table[token_ids.long()].to(torch.int32)
+    return torch.full(idx.shape, 1.0 / table.shape[1], dtype=torch.float32), idx
+
+
+def scale_rows(x, scale):
+    x *= scale
+    return x
