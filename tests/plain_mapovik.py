@@ -11,11 +11,24 @@ Notation: h is a sublayer's input [T, width]; W x means x @ W.T for a stored [ou
 """
 from __future__ import annotations
 
+import json
 import math
+import os
 
 import torch
 
 F64 = torch.float64
+
+
+def read_model_folder(path):
+    """(config.json as a dict, name -> tensor) of a model folder."""
+    from inferx_b200.weights.safetensors_io import Checkpoint
+    with open(os.path.join(path, "config.json")) as f:
+        cfg = json.load(f)
+    ck = Checkpoint(path)
+    w = {n: ck.get(n).clone() for n in ck.names()}
+    ck.close()
+    return cfg, w
 
 
 def _w(weights, name):
@@ -28,6 +41,10 @@ def ident(x):
 
 def round_bf16(x):
     return x.to(torch.bfloat16).to(F64)
+
+
+def round_f32(x):
+    return x.to(torch.float32).to(F64)
 
 
 # -- small functions ---------------------------------------------------------
