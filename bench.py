@@ -847,6 +847,54 @@ def tinapel_configs(z, layers, pattern):
     return new, twin
 
 
+# `--designs --design mapovik`: the Mapovik design (attention beside a state-space mixer, the
+# delta rule with a decay per key channel, experts chosen by a table) beside the Tinapel
+# design at equal width, depth, heads, state sizes, experts and feed-forward widths: a
+# "parallel" layer stands beside Tinapel's attention layer with the same heads, a "delta"
+# layer beside its gated linear attention with a state of the same size.
+MAPOVIK_SIZES = {
+    # attention heads of 128 (keys and values) over `kv` key/value heads; state-space heads
+    # of 64 values with 128 state entries; delta heads with 64 key and 128 value entries
+    "1k": dict(width=1024, heads=8, kv=2, experts=16, top=2, ff=512),
+    "2k": dict(width=2048, heads=16, kv=4, experts=32, top=4, ff=1024),
+    "4k": dict(width=4096, heads=32, kv=8, experts=32, top=4, ff=1408),
+}
+
+
+def mapovik_configs(z, layers, pattern):
+    import math
+    W = z["width"]
+    mlp = {"kind": "moe", "expert": {"ff": z["ff"]},
+           "router": {"experts": z["experts"], "top": z["top"]}}
+    twin_mlp = {"kind": "moe", "expert": {"ff": z["ff"]},
+                "router": {"experts": z["experts"], "top": z["top"], "scale": 1.0}}
+    kinds = {
+        "parallel": {"type": "parallel", "mixer": {
+            "left": {"heads": z["heads"], "kv_heads": z["kv"], "dim": 128, "vdim": 128,
+                     "scale": 1.0 / math.sqrt(128.0),
+                     "rot": {"dims": 64, "base": 10000.0, "scaling": {"factor": 2.0}}},
+            "right": {"heads": W // 64, "vdim": 64, "state": 128, "groups": 2, "conv": 4,
+                      "norm_groups": 2}}, "mlp": mlp},
+        "delta": {"type": "channel_delta", "mixer": {
+            "heads": W // 128, "kv_heads": W // 128, "dim": 64, "vdim": 128, "conv": 4,
+            "rank": 64, "gate_rank": 64}, "mlp": mlp},
+    }
+    twins = {
+        "parallel": {"type": "attention",
+                     "mixer": {"heads": z["heads"], "kv_heads": z["kv"], "dim": 128, "vdim": 128,
+                               "scale": 1.0 / math.sqrt(128.0)}, "mlp": twin_mlp},
+        "delta": {"type": "gla", "mixer": {"heads": W // 128, "dim": 64, "vdim": 128, "tau": 8.0,
+                                           "rank": 64}, "mlp": twin_mlp},
+    }
+    new = {"architecture": "Mapovik", "vocab": DESIGN_VOCAB, "width": W, "norm": {"eps": 1e-5},
+           "residual_mult": 0.5, "logit_scale": 1.0,
+           "layers": [kinds[pattern[i % len(pattern)]] for i in range(layers)]}
+    twin = {"architecture": "Tinapel", "vocab": DESIGN_VOCAB, "width": W,
+            "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+            "layers": [twins[pattern[i % len(pattern)]] for i in range(layers)]}
+    return new, twin
+
+
 def designs(args):
     """One JSON line per size: prompt tokens/s (one prompt of --prefill-tokens, default
     2048) and decode tokens/s (--batch sequences at --context) of both designs, device
@@ -856,15 +904,22 @@ def designs(args):
     prompt = args.prefill_tokens or 2048
     B = args.batch
     tinapel = args.design == "tinapel"
-    sizes = TINAPEL_SIZES if tinapel else DESIGN_SIZES
-    first, second = ("tinapel", "qwen2_moe") if tinapel else ("zuzisun", "qwen2_dense")
+    mapovik = args.design == "mapovik"
+    sizes = MAPOVIK_SIZES if mapovik else TINAPEL_SIZES if tinapel else DESIGN_SIZES
+    first, second = (("mapovik", "tinapel") if mapovik else ("tinapel", "qwen2_moe") if tinapel
+                     else ("zuzisun", "qwen2_dense"))
     for name in (args.design_sizes.split(",") if args.design_sizes else list(sizes)):
         z = sizes[name]
         C = args.context or 4096
         row = {"size": name, "layers": layers, "width": z["width"], "heads": z["heads"],
                "ff": z["ff"], "prompt_tokens": prompt, "batch": B,
                "context": C, "dtype": "bf16", "data": "synthetic, random weights"}
-        if tinapel:
+        if mapovik:
+            pattern = (args.design_pattern if "wkv" not in args.design_pattern
+                       else "parallel,delta,delta,parallel").split(",")
+            row["pattern"] = pattern
+            pair = mapovik_configs(z, layers, pattern)
+        elif tinapel:
             pattern = args.design_pattern.split(",")
             row["pattern"] = pattern
             pair = tinapel_configs(z, layers, pattern)
@@ -936,10 +991,12 @@ def main(argv=None):
                          "beside the closest Qwen2-MoE at equal sizes (random weights); --layers (4), "
                          "--batch, --context (4096), --prefill-tokens (2048) apply")
     ap.add_argument("--design-sizes", default="", help="with --designs: of 1k,2k,4k (all)")
-    ap.add_argument("--design", default="zuzisun", choices=["zuzisun", "tinapel"],
+    ap.add_argument("--design", default="zuzisun", choices=["zuzisun", "tinapel", "mapovik"],
                     help="with --designs: which design stands beside its closest model")
     ap.add_argument("--design-pattern", default="wkv,gla,attention,attention",
-                    help="with --design tinapel: the mixers of the layers, repeated")
+                    help="with --design tinapel: the mixers of the layers, repeated; with "
+                         "--design mapovik of parallel, delta (default "
+                         "parallel,delta,delta,parallel)")
     args = ap.parse_args(argv)
     if args.impl == "reference":
         return reference_arm()

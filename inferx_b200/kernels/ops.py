@@ -1631,15 +1631,17 @@ def causal_conv(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
     """Causal convolution over time per channel with the activation: x [T, C] (a view with
     unit inner stride), ``w`` fp32 [C, taps] whose last column multiplies the current
     token, ``bias`` fp32 [C] or None, ``state`` fp32 [slots, taps - 1, C]: a request's last
-    taps - 1 inputs, read for the tokens before this step's first and moved on.  Returns
+    taps - 1 inputs, read for the tokens before this step's first and moved on (None with
+    one tap, which keeps nothing).  Returns
     [T, C] in x's element type."""
     _chk("w", w, torch.float32)
     _chk("bias", bias, torch.float32, optional=True)
-    _chk("state", state, torch.float32)
     C, taps = w.shape
+    _chk("state", state, torch.float32, optional=taps == 1)
     ldx = _row_view("causal_conv: x", x, C)
     T = x.shape[0]
-    if tuple(state.shape[1:]) != (taps - 1, C) or (bias is not None and bias.numel() != C):
+    if (state is not None and tuple(state.shape[1:]) != (taps - 1, C)) or \
+            (bias is not None and bias.numel() != C):
         raise KernelError("causal_conv: state or bias do not fit the channels and taps")
     out = torch.empty((T, C), dtype=x.dtype, device=x.device)
     _check(_lib().ix_causal_conv(
