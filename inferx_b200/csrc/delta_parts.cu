@@ -231,14 +231,30 @@ __device__ __forceinline__ float softplus_f(float z) {
 
 // state space: q = C, k = dt * B, scalar decay a = exp(-exp(A) dt), skip D x.  Slices do
 // not interact inside a token, so they meet once per chunk.
-template <typename TA, int KPT>
+//
+// Three forms of the walk, as in the linear recurrence with a decay per key channel:
+//   whole    a block walks all of its sequence's tokens of the step, from the state in the
+//            slot to the state it leaves there.
+//   local    long prompts are cut into segments of seg_len tokens that are walked side by
+//            side (grid.x = value tiles * segments).  The first pass walks every segment
+//            but a sequence's last from a zero state, without outputs, and leaves in scratch
+//            the state it ends with and the product of its decays (entry seg + 1); entry 0
+//            takes the state from the slot.
+//   joined   the second pass rebuilds a segment's start state from the entries before it,
+//            S <- P_i S + S_i in ascending i, walks the segment with outputs, and the last
+//            segment leaves the state.  Against the whole walk the results differ by
+//            rounding only.
+enum { RC_WHOLE = 0, RC_LOCAL = 1, RC_JOINED = 2 };
+
+template <typename TA, int KPT, int MODE>
 __global__ void __launch_bounds__(RC_COLS * 8)
 ssd_recurrence_kernel(const TA* __restrict__ xbc, long long ld, const TA* __restrict__ dt_raw,
                       long long ld_dt, const float* __restrict__ dt_bias,
                       const float* __restrict__ a_log, const float* __restrict__ d_skip,
                       float* __restrict__ state, const int* __restrict__ cu_q,
                       const int* __restrict__ state_slot, float* __restrict__ out, int H, int V,
-                      int K, int G, int KS) {
+                      int K, int G, int KS, int seg_len, int nseg, float* __restrict__ scr_s,
+                      float* __restrict__ scr_p) {
   extern __shared__ __align__(16) float sm[];
   float* c_s = sm;                          // [RC_CHUNK][K]   C_t
   float* k_s = c_s + RC_CHUNK * K;          // [RC_CHUNK][K]   dt * B_t
@@ -247,22 +263,51 @@ ssd_recurrence_kernel(const TA* __restrict__ xbc, long long ld, const TA* __rest
   float* part = a_s + RC_CHUNK;             // [KS][RC_CHUNK][RC_COLS]
   IX_PDL_WAIT();
   const int lane = threadIdx.x & 31, ks = threadIdx.x >> 5;
-  const int v0 = blockIdx.x * RC_COLS, h = blockIdx.y, s = blockIdx.z;
+  const int vtiles = (V + RC_COLS - 1) / RC_COLS;
+  const int seg = blockIdx.x / vtiles;
+  const int v0 = (blockIdx.x % vtiles) * RC_COLS, h = blockIdx.y, s = blockIdx.z;
   const int col = v0 + lane;
   const bool col_ok = col < V;
   const int g = h / (H / G);
   const int inner = H * V;
-  const int t_begin = cu_q[s], t_end = cu_q[s + 1];
-  if (t_end <= t_begin) return;
+  const int seq_begin = cu_q[s], seq_end = cu_q[s + 1];
+  if (seq_end <= seq_begin) return;
+  const int nseg_s = MODE == RC_WHOLE ? 1 : (seq_end - seq_begin + seg_len - 1) / seg_len;
+  if (seg >= nseg_s) return;
+  const int t_begin = MODE == RC_WHOLE ? seq_begin : seq_begin + seg * seg_len;
+  const int t_end = MODE == RC_WHOLE ? seq_end : min(seq_end, t_begin + seg_len);
   float* st = state + ((size_t)state_slot[s] * H + h) * K * V;
+  float* my_s = scr_s + ((size_t)s * H + h) * nseg * K * V;   // entries of this (sequence, head)
+  float* my_p = scr_p + ((size_t)s * H + h) * nseg;
+  const bool walks = MODE != RC_LOCAL || seg < nseg_s - 1;
   const int kk0 = ks * KPT;
   const float neg_a = -expf(a_log[h]), bias = dt_bias[h], dsk = d_skip[h];
   float S[KPT];
+  float P = 1.f;
 #pragma unroll
   for (int i = 0; i < KPT; ++i) {
     const int kk = kk0 + i;
-    S[i] = (kk < K && col_ok) ? st[(size_t)kk * V + col] : 0.f;
+    const bool ok = kk < K && col_ok;
+    if (MODE == RC_WHOLE) {
+      S[i] = ok ? st[(size_t)kk * V + col] : 0.f;
+    } else if (MODE == RC_LOCAL) {
+      if (seg == 0 && ok) my_s[(size_t)kk * V + col] = st[(size_t)kk * V + col];
+      S[i] = 0.f;
+    } else {
+      S[i] = ok ? my_s[(size_t)kk * V + col] : 0.f;
+    }
   }
+  if (MODE == RC_JOINED) {
+    for (int e = 1; e <= seg; ++e) {
+      const float pe = my_p[e];
+#pragma unroll
+      for (int i = 0; i < KPT; ++i) {
+        const int kk = kk0 + i;
+        if (kk < K && col_ok) S[i] = pe * S[i] + my_s[((size_t)e * K + kk) * V + col];
+      }
+    }
+  }
+  if (!walks) return;
   for (int t0 = t_begin; t0 < t_end; t0 += RC_CHUNK) {
     const int n = min(RC_CHUNK, t_end - t0);
     if (threadIdx.x < n) {
@@ -275,13 +320,27 @@ ssd_recurrence_kernel(const TA* __restrict__ xbc, long long ld, const TA* __rest
       const int c = i / K, kk = i - c * K;
       const TA* row = xbc + (size_t)(t0 + c) * ld + inner + (size_t)g * K + kk;
       k_s[i] = __fmul_rn(part[c], to_f32(row[0]));
-      c_s[i] = to_f32(row[(size_t)G * K]);
+      if (MODE != RC_LOCAL) c_s[i] = to_f32(row[(size_t)G * K]);
     }
     for (int i = threadIdx.x; i < n * RC_COLS; i += blockDim.x) {
       const int c = i / RC_COLS, j = i - c * RC_COLS;
       v_s[i] = (v0 + j < V) ? to_f32(xbc[(size_t)(t0 + c) * ld + (size_t)h * V + v0 + j]) : 0.f;
     }
     __syncthreads();
+    if (MODE == RC_LOCAL) {
+      // the segment's own state and the product of its decays; nothing is read out
+#pragma unroll 2
+      for (int c = 0; c < n; ++c) {
+        const float vj = v_s[c * RC_COLS + lane], a = a_s[c];
+        const float* kc = k_s + c * K + kk0;
+        P *= a;
+#pragma unroll
+        for (int i = 0; i < KPT; ++i)
+          if (kk0 + i < K) S[i] = __fmaf_rn(a, S[i], __fmul_rn(kc[i], vj));
+      }
+      __syncthreads();
+      continue;
+    }
 #pragma unroll 2
     for (int c = 0; c < n; ++c) {
       const float vj = v_s[c * RC_COLS + lane], a = a_s[c];
@@ -308,6 +367,16 @@ ssd_recurrence_kernel(const TA* __restrict__ xbc, long long ld, const TA* __rest
     }
     __syncthreads();
   }
+  if (MODE == RC_LOCAL) {
+#pragma unroll
+    for (int i = 0; i < KPT; ++i) {
+      const int kk = kk0 + i;
+      if (kk < K && col_ok) my_s[((size_t)(seg + 1) * K + kk) * V + col] = S[i];
+    }
+    if (v0 == 0 && threadIdx.x == 0) my_p[seg + 1] = P;
+    return;
+  }
+  if (MODE == RC_JOINED && seg != nseg_s - 1) return;
 #pragma unroll
   for (int i = 0; i < KPT; ++i) {
     const int kk = kk0 + i;
@@ -433,34 +502,57 @@ IX_API int ix_delta_recurrence_max_dim() { return 8 * 64; }
 
 static inline int rc_slices(int K) { return K > 32 ? 8 : (K > 8 ? 4 : 1); }
 
+// Floats of scratch the segmented state-space walk needs.
+IX_API long long ix_ssd_recurrence_scratch_floats(int S, int H, int K, int V, int nseg) {
+  return nseg <= 1 ? 0 : (long long)S * H * nseg * ((long long)K * V + 1);
+}
+
+// seg_len, nseg: 0, 1 for the walk from end to end; otherwise every sequence is cut into
+// segments of seg_len tokens (nseg covers the longest) and `scratch` holds
+// ix_ssd_recurrence_scratch_floats floats.
 IX_API int ix_ssd_recurrence(const void* xbc, long long ld, const void* dt_raw, long long ld_dt,
                              int dtype, const float* dt_bias, const float* a_log,
                              const float* d_skip, float* state, const int* cu_q,
                              const int* state_slot, float* out, int S, int H, int V, int K, int G,
-                             cudaStream_t stream) {
+                             int seg_len, int nseg, float* scratch, cudaStream_t stream) {
   if (S <= 0) return IX_OK;
   if (H <= 0 || V <= 0 || K <= 0 || G <= 0 || H % G || K > 8 * 64 || H > 65535 || S > 65535)
     return IX_ERR_SIZE;
   if (ld < (long long)H * V + 2LL * G * K || ld_dt < H) return IX_ERR_SIZE;
+  if (nseg < 1 || (nseg > 1 && (seg_len <= 0 || !scratch))) return IX_ERR_SIZE;
   const int KS = rc_slices(K);
   const int kpt = (K + KS - 1) / KS;
   const size_t smem = ((size_t)2 * RC_CHUNK * K + RC_CHUNK * RC_COLS + RC_CHUNK +
                        (size_t)KS * RC_CHUNK * RC_COLS) * sizeof(float);
   if (smem > 200 * 1024) return IX_ERR_SMEM;
-  dim3 grid((V + RC_COLS - 1) / RC_COLS, H, S), block(RC_COLS * KS);
-#define SSD_GO(KPT)                                                                          \
+  const int vtiles = (V + RC_COLS - 1) / RC_COLS;
+  dim3 grid(vtiles * nseg, H, S), block(RC_COLS * KS);
+  float* scr_s = scratch;
+  float* scr_p = scratch ? scratch + (size_t)S * H * nseg * K * V : nullptr;
+#define SSD_ONE(KPT, MODE)                                                                   \
   IX_DISPATCH_DTYPE(dtype, TA, {                                                             \
-    auto kern = ssd_recurrence_kernel<TA, KPT>;                                              \
+    auto kern = ssd_recurrence_kernel<TA, KPT, MODE>;                                        \
     if (smem > 48 * 1024)                                                                    \
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
     ix_launch(kern, grid, block, smem, stream, (const TA*)xbc, ld, (const TA*)dt_raw, ld_dt, \
-              dt_bias, a_log, d_skip, state, cu_q, state_slot, out, H, V, K, G, KS);         \
+              dt_bias, a_log, d_skip, state, cu_q, state_slot, out, H, V, K, G, KS, seg_len, \
+              nseg, scr_s, scr_p);                                                           \
   })
+#define SSD_GO(KPT)                                                                          \
+  do {                                                                                       \
+    if (nseg <= 1) {                                                                         \
+      SSD_ONE(KPT, RC_WHOLE);                                                                \
+    } else {                                                                                 \
+      SSD_ONE(KPT, RC_LOCAL);                                                                \
+      SSD_ONE(KPT, RC_JOINED);                                                               \
+    }                                                                                        \
+  } while (0)
   if (kpt <= 8) SSD_GO(8);
   else if (kpt <= 16) SSD_GO(16);
   else if (kpt <= 32) SSD_GO(32);
   else SSD_GO(64);
 #undef SSD_GO
+#undef SSD_ONE
   return ix_launch_status();
 }
 

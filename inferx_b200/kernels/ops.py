@@ -1672,12 +1672,18 @@ def ssd_recurrence(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tenso
             not (dt_bias.numel() == a_log.numel() == d_skip.numel() == heads):
         raise KernelError("ssd_recurrence: inputs and state do not fit together")
     out = torch.empty((T, heads * vdim), dtype=torch.float32, device=xbc.device)
+    seg_len, nseg = recurrence_segments(int(getattr(step, "max_q_len", 0) or T), step.num_seqs,
+                                        heads, vdim)
+    scratch = None
+    if nseg > 1:
+        scratch = torch.empty((_lib().ix_ssd_recurrence_scratch_floats(
+            step.num_seqs, heads, nstate, vdim, nseg),), dtype=torch.float32, device=xbc.device)
     _check(_lib().ix_ssd_recurrence(
         _ptr(xbc), ctypes.c_longlong(ld), _ptr(dt_raw), ctypes.c_longlong(ld_dt),
         _dtype_code(xbc), _ptr(dt_bias), _ptr(a_log), _ptr(d_skip), _ptr(state), _ptr(step.cu_q),
-        _ptr(step.state_slot), _ptr(out), step.num_seqs, heads, vdim, nstate, groups, _stream()),
-        "ssd_recurrence")
-    _count()
+        _ptr(step.state_slot), _ptr(out), step.num_seqs, heads, vdim, nstate, groups, seg_len,
+        nseg, _ptr(scratch), _stream()), "ssd_recurrence")
+    _count(2 if nseg > 1 else 1)
     return out
 
 

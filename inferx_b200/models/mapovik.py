@@ -16,8 +16,11 @@ pass the stream x becomes ``loop.in`` [x; x0] (x0 the embedding output) and row 
 ``loop.step``, and per layer i ``l<i>.norm1``, ``l<i>.norm2``, ``l<i>.mix.*``,
 ``l<i>.mlp.*``.
 
-Scores, softmax weights and their products with the values stay in 32-bit arithmetic in
-this design, so its attention asks for the fp32-arithmetic kernels in every element type.
+Scores, maxima, sums and softmax weights are 32-bit in every attention kernel.  Heads whose
+values have the keys' size and an even one run on the kernels the other models use (in
+bfloat16 the tensor-core kernels, where the weights enter their product with the values as
+bfloat16 operands of a matrix product with 32-bit accumulation); every other shape, and
+every 32-bit run, on the fp32-arithmetic kernels.
 """
 from __future__ import annotations
 
@@ -36,10 +39,11 @@ def _mixer(cfg: MapovikConfig, layer):
         a, s = layer.left, layer.right
         position = (RopeSpec(head_dim=a.dim, rotary_dim=a.rot_dims, theta=a.rot_base,
                              scaling_factor=a.rot_factor) if a.rot_dims else None)
+        general = a.vdim != a.dim or a.dim % 2 == 1
         left = AttentionSpec(
             hidden=cfg.width, heads=a.heads, kv_heads=a.kv_heads, head_dim=a.dim,
             qkv_bias=False, scale=a.scale, window=0, position=position,
-            value_dim=a.vdim if a.vdim != a.dim else 0, fp32_weights=True, out_float32=True,
+            value_dim=a.vdim if a.vdim != a.dim else 0, fp32_weights=general, out_float32=True,
             names=("q", "k", "v", "o"))
         right = StateSpaceSpec(hidden=cfg.width, heads=s.heads, vdim=s.vdim, state=s.state,
                                groups=s.groups, conv=s.conv, norm_groups=s.norm_groups,

@@ -92,7 +92,7 @@ MD = {
                  ssd(8, 64, 64, 2, 4, 4), moe(8, 2, 128)),
         delta(4, 2, 64, 128, 4, rank=16, gate_rank=16, mlp=moe(8, 2, 128)),
         delta(2, 2, 128, 64, 4, rank=32, gate_rank=8, mlp=dense(512)),
-        parallel(attention(4, 1, 128, 128, 0.09, rot=(128, 1e6, None)), ssd(4, 32, 128, 1, 4, 1),
+        parallel(attention(4, 1, 128, 128, 0.09, rot=(64, 1e6, 3.0)), ssd(4, 32, 128, 1, 4, 1),
                  dense(384)),
     ],
     "loop": {"start": 0, "stop": 4, "times": 2},

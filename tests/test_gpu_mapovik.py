@@ -176,6 +176,38 @@ def test_state_space_recurrence(dtype, H, V, N, G):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,V,N,G", [(2, 40, 24, 1), (4, 64, 128, 2), (3, 5, 7, 3)])
+def test_state_space_recurrence_in_segments(dtype, H, V, N, G):
+    """Long prompts are walked in segments side by side and joined: a long prompt beside a
+    single token and a portion that continues a state, against the plain walk and against the
+    same tokens in portions too short to be cut."""
+    g = torch.Generator().manual_seed(H + V + N)
+    q_lens = [700, 1, 131]
+    step = _step(q_lens, [0, 40, 64], slots=[2, 0, 1])
+    T = sum(q_lens)
+    width = H * V + 2 * G * N
+    xbc = (torch.randn(T, width, generator=g) * 0.7).to(dtype)
+    dt = torch.randn(T, H, generator=g).to(dtype)
+    dt_bias, a_log, d_skip = (torch.randn(H, generator=g) for _ in range(3))
+    a_log -= 2.0                                   # decays near 1: far tokens stay in the state
+    state = torch.randn(3, H, N, V, generator=g)
+    st_ref = state.clone()
+    ref = host_ops.ssd_recurrence(xbc, dt, dt_bias, a_log, d_skip, st_ref, step, H, V, N, G)
+    hp = [t.cuda() for t in (dt_bias, a_log, d_skip)]
+    st = state.cuda()
+    out = _ops().ssd_recurrence(xbc.cuda(), dt.cuda(), *hp, st, _cuda(step), H, V, N, G)
+    assert _rel(out.cpu(), ref) <= 3e-5 and _rel(st.cpu(), st_ref) <= 3e-5
+    st2, at, outs = state.cuda(), 0, []
+    while at < 700:
+        n = min(100, 700 - at)
+        outs.append(_ops().ssd_recurrence(xbc[at:at + n].cuda(), dt[at:at + n].cuda(), *hp, st2,
+                                          _cuda(_step([n], [at], [2])), H, V, N, G))
+        at += n
+    assert _rel(torch.cat(outs).cpu(), out[:700].cpu()) <= 1e-5
+    assert _rel(st2[2].cpu(), st[2].cpu()) <= 1e-5
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,HK,K,V", [(4, 4, 32, 48), (4, 2, 12, 20), (6, 3, 5, 9), (2, 1, 128, 64),
                                       (3, 1, 7, 5), (2, 2, 64, 128), (1, 1, 24, 100)])
 def test_delta_recurrence(dtype, H, HK, K, V):
