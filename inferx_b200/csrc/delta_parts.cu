@@ -387,7 +387,19 @@ ssd_recurrence_kernel(const TA* __restrict__ xbc, long long ld, const TA* __rest
 // gated delta rule.  With D = diag(g) S: u = beta (v - D^T k), o = D^T q + (k . q) u,
 // S = D + k u^T: the slices' partial sums of D^T k and D^T q meet once per token.  q and k
 // are made unit vectors (q also times q_scale) while a chunk is staged.
-template <typename TA, int KPT>
+//
+// A token's step is linear in the state, S_t = A_t S_(t-1) + beta_t k_t v_t^T with
+// A_t = (I - beta_t k_t k_t^T) diag(g_t), so long prompts are walked in segments side by
+// side like the other recurrences, with a matrix where those have a product of decays:
+//   local    every segment but a sequence's last is walked from a zero state without
+//            outputs (its own state, entry seg + 1 of `scr_s`), and the same walk over the
+//            columns of the identity matrix with values of zero gives the product of its
+//            A_t (entry seg + 1 of `scr_a`, [K, K]); entry 0 of `scr_s` takes the slot's state.
+//   joined   a segment's start state is rebuilt from the entries before it,
+//            S <- A_i S + S_i in ascending i, the segment is walked with outputs, and the
+//            last segment leaves the state.  Against the whole walk the results differ by
+//            rounding only.
+template <typename TA, int KPT, int MODE>
 __global__ void __launch_bounds__(RC_COLS * 8)
 delta_recurrence_kernel(const TA* __restrict__ q, long long ldq, const TA* __restrict__ k,
                         long long ldk, const TA* __restrict__ v, long long ldv,
@@ -395,30 +407,88 @@ delta_recurrence_kernel(const TA* __restrict__ q, long long ldq, const TA* __res
                         const float* __restrict__ decay, float* __restrict__ state,
                         const int* __restrict__ cu_q, const int* __restrict__ state_slot,
                         float* __restrict__ out, int H, int HK, int K, int V, int KS,
-                        float unit_eps, float q_scale) {
+                        float unit_eps, float q_scale, int seg_len, int nseg,
+                        float* __restrict__ scr_s, float* __restrict__ scr_a) {
   extern __shared__ __align__(16) float sm[];
-  float* q_s = sm;                          // [RC_CHUNK][K]
-  float* k_s = q_s + RC_CHUNK * K;          // [RC_CHUNK][K]
-  float* g_s = k_s + RC_CHUNK * K;          // [RC_CHUNK][K]
-  float* v_s = g_s + RC_CHUNK * K;          // [RC_CHUNK][RC_COLS]
+  // rows of KP = KS * KPT entries: the entries from K on stay zero, so that every slice
+  // reads its KPT entries of a token as whole float4 without asking where the head ends
+  const int KP = KS * KPT;
+  float* q_s = sm;                          // [RC_CHUNK][KP]
+  float* k_s = q_s + RC_CHUNK * KP;         // [RC_CHUNK][KP]
+  float* g_s = k_s + RC_CHUNK * KP;         // [RC_CHUNK][KP]
+  float* v_s = g_s + RC_CHUNK * KP;         // [RC_CHUNK][RC_COLS]
   float* b_s = v_s + RC_CHUNK * RC_COLS;    // [RC_CHUNK] beta
   float* kq_s = b_s + RC_CHUNK;             // [RC_CHUNK] k . q
   float* part = kq_s + RC_CHUNK;            // [2][KS][2][RC_COLS]
   IX_PDL_WAIT();
   const int lane = threadIdx.x & 31, ks = threadIdx.x >> 5;
-  const int v0 = blockIdx.x * RC_COLS, h = blockIdx.y, s = blockIdx.z;
+  const int vtiles = (V + RC_COLS - 1) / RC_COLS;
+  const int tiles = vtiles + (MODE == RC_LOCAL ? (K + RC_COLS - 1) / RC_COLS : 0);
+  const int seg = blockIdx.x / tiles, tile = blockIdx.x % tiles;
+  const bool a_tile = tile >= vtiles;       // columns of the segment's transition matrix
+  const int v0 = (a_tile ? tile - vtiles : tile) * RC_COLS, h = blockIdx.y, s = blockIdx.z;
   const int col = v0 + lane;
-  const bool col_ok = col < V;
+  const bool col_ok = col < (a_tile ? K : V);
   const int j = h / (H / HK);
-  const int t_begin = cu_q[s], t_end = cu_q[s + 1];
-  if (t_end <= t_begin) return;
+  const int seq_begin = cu_q[s], seq_end = cu_q[s + 1];
+  if (seq_end <= seq_begin) return;
+  const int nseg_s = MODE == RC_WHOLE ? 1 : (seq_end - seq_begin + seg_len - 1) / seg_len;
+  if (seg >= nseg_s) return;
+  const int t_begin = MODE == RC_WHOLE ? seq_begin : seq_begin + seg * seg_len;
+  const int t_end = MODE == RC_WHOLE ? seq_end : min(seq_end, t_begin + seg_len);
   float* st = state + ((size_t)state_slot[s] * H + h) * K * V;
+  float* my_s = scr_s + ((size_t)s * H + h) * nseg * K * V;
+  float* my_a = scr_a + ((size_t)s * H + h) * nseg * K * K;
+  const bool walks = MODE != RC_LOCAL || seg < nseg_s - 1;
   const int kk0 = ks * KPT;
   float S[KPT];
 #pragma unroll
   for (int i = 0; i < KPT; ++i) {
     const int kk = kk0 + i;
-    S[i] = (kk < K && col_ok) ? st[(size_t)kk * V + col] : 0.f;
+    const bool ok = kk < K && col_ok;
+    if (MODE == RC_WHOLE) {
+      S[i] = ok ? st[(size_t)kk * V + col] : 0.f;
+    } else if (MODE == RC_LOCAL) {
+      if (!a_tile && seg == 0 && ok) my_s[(size_t)kk * V + col] = st[(size_t)kk * V + col];
+      S[i] = (a_tile && ok && kk == col) ? 1.f : 0.f;
+    } else {
+      S[i] = ok ? my_s[(size_t)kk * V + col] : 0.f;
+    }
+  }
+  if (MODE == RC_JOINED) {
+    float* x_s = q_s;                       // [K][RC_COLS]: the state's columns, all slices'
+    for (int e = 1; e <= seg; ++e) {
+#pragma unroll
+      for (int i = 0; i < KPT; ++i)
+        if (kk0 + i < K) x_s[(kk0 + i) * RC_COLS + lane] = S[i];
+      __syncthreads();
+      const float* A = my_a + (size_t)e * K * K;
+      float acc[KPT];
+#pragma unroll
+      for (int i = 0; i < KPT; ++i) {
+        const int kk = kk0 + i;
+        acc[i] = (kk < K && col_ok) ? my_s[((size_t)e * K + kk) * V + col] : 0.f;
+      }
+      for (int jj = 0; jj < K; ++jj) {
+        const float x = x_s[jj * RC_COLS + lane];
+#pragma unroll
+        for (int i = 0; i < KPT; ++i)
+          if (kk0 + i < K) acc[i] = fmaf(A[(size_t)(kk0 + i) * K + jj], x, acc[i]);
+      }
+      __syncthreads();
+#pragma unroll
+      for (int i = 0; i < KPT; ++i) S[i] = acc[i];
+    }
+  }
+  if (!walks) return;
+  if (KP > K) {
+    const int pad = KP - K;
+    for (int i = threadIdx.x; i < RC_CHUNK * pad; i += blockDim.x) {
+      const int at = (i / pad) * KP + K + i % pad;
+      q_s[at] = 0.f;
+      k_s[at] = 0.f;
+      g_s[at] = 0.f;
+    }
   }
   int buf = 0;
   for (int t0 = t_begin; t0 < t_end; t0 += RC_CHUNK) {
@@ -426,13 +496,14 @@ delta_recurrence_kernel(const TA* __restrict__ q, long long ldq, const TA* __res
     for (int i = threadIdx.x; i < n * K; i += blockDim.x) {
       const int c = i / K, kk = i - c * K;
       const size_t t = (size_t)(t0 + c);
-      q_s[i] = to_f32(q[t * ldq + (size_t)j * K + kk]);
-      k_s[i] = to_f32(k[t * ldk + (size_t)j * K + kk]);
-      g_s[i] = decay[(t * H + h) * K + kk];
+      if (MODE != RC_LOCAL) q_s[c * KP + kk] = to_f32(q[t * ldq + (size_t)j * K + kk]);
+      k_s[c * KP + kk] = to_f32(k[t * ldk + (size_t)j * K + kk]);
+      g_s[c * KP + kk] = decay[(t * H + h) * K + kk];
     }
     for (int i = threadIdx.x; i < n * RC_COLS; i += blockDim.x) {
       const int c = i / RC_COLS, jj = i - c * RC_COLS;
-      v_s[i] = (v0 + jj < V) ? to_f32(v[(size_t)(t0 + c) * ldv + (size_t)h * V + v0 + jj]) : 0.f;
+      v_s[i] = (!a_tile && v0 + jj < V)
+                   ? to_f32(v[(size_t)(t0 + c) * ldv + (size_t)h * V + v0 + jj]) : 0.f;
     }
     if (threadIdx.x < n) {
       const float z = to_f32(beta_raw[(size_t)(t0 + threadIdx.x) * ldb + h]);
@@ -443,54 +514,83 @@ delta_recurrence_kernel(const TA* __restrict__ q, long long ldq, const TA* __res
     for (int c = ks; c < n; c += KS) {
       float sq = 0.f, sk = 0.f;
       for (int kk = lane; kk < K; kk += 32) {
-        sq = fmaf(q_s[c * K + kk], q_s[c * K + kk], sq);
-        sk = fmaf(k_s[c * K + kk], k_s[c * K + kk], sk);
+        if (MODE != RC_LOCAL) sq = fmaf(q_s[c * KP + kk], q_s[c * KP + kk], sq);
+        sk = fmaf(k_s[c * KP + kk], k_s[c * KP + kk], sk);
       }
-      const float iq = q_scale / sqrtf(warp_sum(sq) + unit_eps);
+      const float iq = MODE != RC_LOCAL ? q_scale / sqrtf(warp_sum(sq) + unit_eps) : 0.f;
       const float ik = 1.0f / sqrtf(warp_sum(sk) + unit_eps);
       float dot = 0.f;
       for (int kk = lane; kk < K; kk += 32) {
-        const float qq = q_s[c * K + kk] * iq, kv = k_s[c * K + kk] * ik;
-        q_s[c * K + kk] = qq;
-        k_s[c * K + kk] = kv;
-        dot = fmaf(qq, kv, dot);
+        const float kv = k_s[c * KP + kk] * ik;
+        k_s[c * KP + kk] = kv;
+        if (MODE != RC_LOCAL) {
+          const float qq = q_s[c * KP + kk] * iq;
+          q_s[c * KP + kk] = qq;
+          dot = fmaf(qq, kv, dot);
+        }
       }
-      dot = warp_sum(dot);
-      if (lane == 0) kq_s[c] = dot;
+      if (MODE != RC_LOCAL) {
+        dot = warp_sum(dot);
+        if (lane == 0) kq_s[c] = dot;
+      }
     }
     __syncthreads();
     for (int c = 0; c < n; ++c) {
-      const float* qc = q_s + c * K + kk0;
-      const float* kc = k_s + c * K + kk0;
-      const float* gc = g_s + c * K + kk0;
+      const float4* g4 = reinterpret_cast<const float4*>(g_s + c * KP + kk0);
+      const float4* k4 = reinterpret_cast<const float4*>(k_s + c * KP + kk0);
+      const float4* q4 = reinterpret_cast<const float4*>(q_s + c * KP + kk0);
       float pk = 0.f, pq = 0.f;
 #pragma unroll
-      for (int i = 0; i < KPT; ++i) {
-        if (kk0 + i < K) {
-          S[i] = __fmul_rn(gc[i], S[i]);
-          pk = __fmaf_rn(S[i], kc[i], pk);
-          pq = __fmaf_rn(S[i], qc[i], pq);
+      for (int i = 0; i < KPT; i += 4) {
+        const float4 gv = g4[i / 4], kv = k4[i / 4];
+        const float gc[4] = {gv.x, gv.y, gv.z, gv.w}, kc[4] = {kv.x, kv.y, kv.z, kv.w};
+        float qc[4] = {0.f, 0.f, 0.f, 0.f};
+        if (MODE != RC_LOCAL) {
+          const float4 qv = q4[i / 4];
+          qc[0] = qv.x, qc[1] = qv.y, qc[2] = qv.z, qc[3] = qv.w;
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          S[i + e] = __fmul_rn(gc[e], S[i + e]);
+          pk = __fmaf_rn(S[i + e], kc[e], pk);
+          if (MODE != RC_LOCAL) pq = __fmaf_rn(S[i + e], qc[e], pq);
         }
       }
       float* pb = part + (size_t)buf * KS * 2 * RC_COLS;
       pb[(ks * 2 + 0) * RC_COLS + lane] = pk;
-      pb[(ks * 2 + 1) * RC_COLS + lane] = pq;
+      if (MODE != RC_LOCAL) pb[(ks * 2 + 1) * RC_COLS + lane] = pq;
       __syncthreads();
       float kd = 0.f, qd = 0.f;
-      for (int w = 0; w < KS; ++w) {
-        kd += pb[(w * 2 + 0) * RC_COLS + lane];
-        qd += pb[(w * 2 + 1) * RC_COLS + lane];
-      }
+      for (int w = 0; w < KS; ++w) kd += pb[(w * 2 + 0) * RC_COLS + lane];
+      if (MODE != RC_LOCAL && ks == 0)      // the first slice writes the outputs
+        for (int w = 0; w < KS; ++w) qd += pb[(w * 2 + 1) * RC_COLS + lane];
       const float u = __fmul_rn(b_s[c], v_s[c * RC_COLS + lane] - kd);
 #pragma unroll
-      for (int i = 0; i < KPT; ++i)
-        if (kk0 + i < K) S[i] = __fmaf_rn(kc[i], u, S[i]);
-      if (ks == 0 && col_ok)
+      for (int i = 0; i < KPT; i += 4) {
+        const float4 kv = k4[i / 4];
+        S[i] = __fmaf_rn(kv.x, u, S[i]);
+        S[i + 1] = __fmaf_rn(kv.y, u, S[i + 1]);
+        S[i + 2] = __fmaf_rn(kv.z, u, S[i + 2]);
+        S[i + 3] = __fmaf_rn(kv.w, u, S[i + 3]);
+      }
+      if (MODE != RC_LOCAL && ks == 0 && col_ok)
         out[((size_t)(t0 + c) * H + h) * V + col] = __fmaf_rn(kq_s[c], u, qd);
       buf ^= 1;
     }
     __syncthreads();
   }
+  if (MODE == RC_LOCAL) {
+#pragma unroll
+    for (int i = 0; i < KPT; ++i) {
+      const int kk = kk0 + i;
+      if (kk < K && col_ok) {
+        if (a_tile) my_a[((size_t)(seg + 1) * K + kk) * K + col] = S[i];
+        else my_s[((size_t)(seg + 1) * K + kk) * V + col] = S[i];
+      }
+    }
+    return;
+  }
+  if (MODE == RC_JOINED && seg != nseg_s - 1) return;
 #pragma unroll
   for (int i = 0; i < KPT; ++i) {
     const int kk = kk0 + i;
@@ -556,36 +656,61 @@ IX_API int ix_ssd_recurrence(const void* xbc, long long ld, const void* dt_raw, 
   return ix_launch_status();
 }
 
+// Floats of scratch the segmented delta walk needs.
+IX_API long long ix_delta_recurrence_scratch_floats(int S, int H, int K, int V, int nseg) {
+  return nseg <= 1 ? 0 : (long long)S * H * nseg * ((long long)K * V + (long long)K * K);
+}
+
+// seg_len, nseg: 0, 1 for the walk from end to end; otherwise every sequence is cut into
+// segments of seg_len tokens (nseg covers the longest) and `scratch` holds
+// ix_delta_recurrence_scratch_floats floats.
 IX_API int ix_delta_recurrence(const void* q, long long ldq, const void* k, long long ldk,
                                const void* v, long long ldv, const void* beta_raw, long long ldb,
                                int dtype, const float* decay, float* state, const int* cu_q,
                                const int* state_slot, float* out, int S, int H, int HK, int K,
-                               int V, float unit_eps, float q_scale, cudaStream_t stream) {
+                               int V, float unit_eps, float q_scale, int seg_len, int nseg,
+                               float* scratch, cudaStream_t stream) {
   if (S <= 0) return IX_OK;
   if (H <= 0 || HK <= 0 || H % HK || K <= 0 || V <= 0 || K > 8 * 64 || H > 65535 || S > 65535)
     return IX_ERR_SIZE;
   if (ldq < (long long)HK * K || ldk < (long long)HK * K || ldv < (long long)H * V || ldb < H)
     return IX_ERR_SIZE;
+  if (nseg < 1 || (nseg > 1 && (seg_len <= 0 || !scratch))) return IX_ERR_SIZE;
   const int KS = rc_slices(K);
   const int kpt = (K + KS - 1) / KS;
-  const size_t smem = ((size_t)3 * RC_CHUNK * K + RC_CHUNK * RC_COLS + 2 * RC_CHUNK +
+  const int kp = KS * (kpt <= 8 ? 8 : kpt <= 16 ? 16 : kpt <= 32 ? 32 : 64);
+  const size_t smem = ((size_t)3 * RC_CHUNK * kp + RC_CHUNK * RC_COLS + 2 * RC_CHUNK +
                        (size_t)2 * KS * 2 * RC_COLS) * sizeof(float);
   if (smem > 200 * 1024) return IX_ERR_SMEM;
-  dim3 grid((V + RC_COLS - 1) / RC_COLS, H, S), block(RC_COLS * KS);
-#define DR_GO(KPT)                                                                           \
+  const int vtiles = (V + RC_COLS - 1) / RC_COLS, atiles = (K + RC_COLS - 1) / RC_COLS;
+  const dim3 block(RC_COLS * KS);
+  float* scr_s = scratch;
+  float* scr_a = scratch ? scratch + (size_t)S * H * nseg * K * V : nullptr;
+#define DR_ONE(KPT, MODE, TILES)                                                             \
   IX_DISPATCH_DTYPE(dtype, TA, {                                                             \
-    auto kern = delta_recurrence_kernel<TA, KPT>;                                            \
+    auto kern = delta_recurrence_kernel<TA, KPT, MODE>;                                      \
     if (smem > 48 * 1024)                                                                    \
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
-    ix_launch(kern, grid, block, smem, stream, (const TA*)q, ldq, (const TA*)k, ldk,         \
-              (const TA*)v, ldv, (const TA*)beta_raw, ldb, decay, state, cu_q, state_slot,   \
-              out, H, HK, K, V, KS, unit_eps, q_scale);                                      \
+    ix_launch(kern, dim3((TILES) * nseg, H, S), block, smem, stream, (const TA*)q, ldq,      \
+              (const TA*)k, ldk, (const TA*)v, ldv, (const TA*)beta_raw, ldb, decay, state,  \
+              cu_q, state_slot, out, H, HK, K, V, KS, unit_eps, q_scale, seg_len, nseg,      \
+              scr_s, scr_a);                                                                 \
   })
+#define DR_GO(KPT)                                                                           \
+  do {                                                                                       \
+    if (nseg <= 1) {                                                                         \
+      DR_ONE(KPT, RC_WHOLE, vtiles);                                                         \
+    } else {                                                                                 \
+      DR_ONE(KPT, RC_LOCAL, vtiles + atiles);                                                \
+      DR_ONE(KPT, RC_JOINED, vtiles);                                                        \
+    }                                                                                        \
+  } while (0)
   if (kpt <= 8) DR_GO(8);
   else if (kpt <= 16) DR_GO(16);
   else if (kpt <= 32) DR_GO(32);
   else DR_GO(64);
 #undef DR_GO
+#undef DR_ONE
   return ix_launch_status();
 }
 

@@ -392,10 +392,107 @@ def recurrent(args):
     return out
 
 
+def delta(args):
+    """The kernels of the convolution-and-state mixers and of the scaled pre-norm arrangement:
+    ``--tokens`` rows of ``--hidden`` as one prompt (``--batch`` 1) or as that many sequences
+    of one token (``--batch`` = ``--tokens``).  State-space heads of 64 values with 128 state
+    entries in 2 groups; delta heads of 64 key and 128 value entries; convolutions of 4 taps.
+    With ``--context``: single-token attention over that many keys for heads of
+    ``--head-dim`` keys and twice as wide values, on the kernel of any size.  Achieved GB/s
+    over the bytes the operation has to move."""
+    from . import ops
+    T, W, B = args.tokens, args.hidden, max(1, args.batch)
+    dt = torch.bfloat16
+    n = max(2, min(8, _copies(T * W * 14)))
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    per = T // B
+    step = types.SimpleNamespace(
+        cu_q=i32([i * per for i in range(B + 1)]), num_seqs=B, max_q_len=per, num_tokens=T,
+        seq_of_token=torch.arange(T, dtype=torch.int32, device="cuda") // per,
+        state_slot=torch.arange(B, dtype=torch.int32, device="cuda"),
+        positions=torch.arange(T, dtype=torch.int32, device="cuda") % per)
+    gain = torch.ones(W, device="cuda")
+    resid = [torch.randn(T, W, device="cuda") for _ in range(n)]
+    d32 = [torch.randn(T, W, device="cuda") for _ in range(n)]
+    x16 = [torch.randn(T, W, device="cuda", dtype=dt) for _ in range(n)]
+    # state space: heads of 64 values, 128 state entries, 2 groups
+    SH, SV, SN, SG = W // 64, 64, 128, 2
+    cw = SH * SV + 2 * SG * SN
+    xbc = [torch.randn(T, cw, device="cuda", dtype=dt) * 0.3 for _ in range(n)]
+    sdt = [torch.randn(T, SH, device="cuda", dtype=dt) for _ in range(n)]
+    hp = [torch.randn(SH, device="cuda") for _ in range(3)]
+    s_states = [torch.zeros(B, SH, SN, SV, device="cuda") for _ in range(n)]
+    conv_w, conv_b = torch.randn(cw, 4, device="cuda"), torch.randn(cw, device="cuda")
+    conv_st = torch.zeros(B, 3, cw, device="cuda")
+    y32 = [torch.randn(T, SH * SV, device="cuda") for _ in range(n)]
+    # delta rule: heads of 64 key and 128 value entries
+    DH, DK, DV = W // 128, 64, 128
+    dq = [torch.randn(2, T, DH * DK, device="cuda", dtype=dt) for _ in range(n)]
+    dv = [torch.randn(T, DH * DV, device="cuda", dtype=dt) for _ in range(n)]
+    beta = [torch.randn(T, DH, device="cuda", dtype=dt) for _ in range(n)]
+    decay = [torch.rand(T, DH * DK, device="cuda") * 0.1 + 0.9 for _ in range(n)]
+    d_states = [torch.zeros(B, DH, DK, DV, device="cuda") for _ in range(n)]
+    R = 64
+    low = [torch.randn(T, R, device="cuda", dtype=dt) for _ in range(n)]
+    w2 = torch.randn(R, DH * DK, device="cuda") * 0.1
+    rate = torch.zeros(DH, device="cuda")
+    o = [torch.randn(T, DH, DV, device="cuda") for _ in range(n)]
+    cases = {
+        "add_scaled_norm(layer norm)": (
+            lambda i: ops.add_scaled_norm(resid[i], d32[i], 0.5, None, gain, 1e-5, dt),
+            (8 + 4 + 2) * T * W),
+        "causal_conv(4 taps, silu)": (
+            lambda i: ops.causal_conv(xbc[i], conv_w, conv_b, conv_st, step), 4 * T * cw),
+        "ssd_recurrence": (
+            lambda i: ops.ssd_recurrence(xbc[i], sdt[i], *hp, s_states[i], step, SH, SV, SN, SG),
+            T * (2 * cw + 4 * SH * SV) + 2 * B * SH * SN * SV * 4),
+        "gated_group_norm": (
+            lambda i: ops.gated_group_norm(y32[i], x16[i][:, :SH * SV], gain[:SH * SV], 2, 1e-5),
+            (4 + 2 + 2) * T * SH * SV),
+        "normed_pair_mean": (
+            lambda i: ops.normed_pair_mean(d32[i], resid[i], gain, gain, 1e-5), 12 * T * W),
+        "lowrank_decay(softplus rate)": (
+            lambda i: ops.lowrank_decay(low[i], w2, torch.zeros_like(w2[0]), "exp_rate_softplus",
+                                        head_log_rate=rate), T * (2 * R + 4 * DH * DK)),
+        "delta_recurrence": (
+            lambda i: ops.delta_recurrence(dq[i][0], dq[i][1], dv[i], beta[i], decay[i],
+                                           d_states[i], step, DH, DH, DK, DV, 1e-6, 0.125),
+            T * DH * (2 * DK * 2 + DK * 4 + DV * 2 + DV * 4) + 2 * B * DH * DK * DV * 4),
+        "head_norm_gate(sigmoid)": (
+            lambda i: ops.head_norm_gate(o[i], gain[:DV], x16[i][:, :DH * DV], 1e-5, dt,
+                                         gate_form="sigmoid"), (4 + 2 + 2) * T * DH * DV),
+    }
+    out = {"case": "delta", "tokens": T, "sequences": B, "hidden": W}
+    for name, (fn, nbytes) in cases.items():
+        us = _time(fn, n, args.iters)
+        out[name] = {"us": round(us, 2), "GBps": round(nbytes / us / 1e3, 1)}
+    out["ssd_recurrence"]["TFLOPs_fp32"] = round(
+        2 * 3 * T * SH * SN * SV / out["ssd_recurrence"]["us"] / 1e6, 2)
+    out["delta_recurrence"]["TFLOPs_fp32"] = round(
+        2 * 4 * T * DH * DK * DV / out["delta_recurrence"]["us"] / 1e6, 2)
+    if args.context:
+        S, C, hd, page = max(1, args.batch), args.context, args.head_dim, args.page
+        heads, kvh, vd = args.heads, args.kv_heads, 2 * args.head_dim
+        blocks = -(-C // page)
+        m = max(2, min(8, _copies(S * kvh * C * (hd + vd) * 2)))
+        kcs = [torch.randn(S * blocks, kvh, page, hd, device="cuda", dtype=dt) for _ in range(m)]
+        vcs = [torch.randn(S * blocks, kvh, page, vd, device="cuda", dtype=dt) for _ in range(m)]
+        bt = torch.arange(S * blocks, dtype=torch.int32, device="cuda").view(S, blocks)
+        kv_len = torch.full((S,), C, dtype=torch.int32, device="cuda")
+        qs = torch.randn(S, heads, hd, device="cuda", dtype=dt)
+        us = _time(lambda i: ops.paged_attention_decode_any(qs, kcs[i], vcs[i], bt, kv_len, C, 0,
+                                                            hd ** -0.5), m, args.iters)
+        nbytes = S * kvh * C * (hd + vd) * 2
+        out["paged_attention_decode_any"] = {
+            "sequences": S, "context": C, "heads": heads, "kv_heads": kvh, "head_dim": hd,
+            "value_dim": vd, "us": round(us, 2), "GBps": round(nbytes / us / 1e3, 1)}
+    return out
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("case", choices=["attn_decode", "grouped", "dense", "attn_prefill", "router",
-                                     "qkv", "latent_attn", "rowwise", "recurrent"])
+                                     "qkv", "latent_attn", "rowwise", "recurrent", "delta"])
     ap.add_argument("--softcap", type=float, default=0.0,
                     help="attn_decode, attn_prefill: squash scores to softcap * tanh(s / softcap)")
     ap.add_argument("--rank", type=int, default=512, help="latent_attn: entries of the latent")

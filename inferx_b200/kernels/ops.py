@@ -822,18 +822,58 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         return paged_attention_prefill(q, k_cache, v_cache, block_table, step.cu_q, step.q_pos0,
                                        window, scale, max_kv_len=step.max_kv_len,
                                        softcap=softcap)
-    if (step.num_tokens >= TILED_ATTENTION_MIN_QUERIES * step.num_seqs
-            and _lib().ix_paged_attention_tiled_applies(hd)
-            and getattr(step, "cu_q", None) is not None):
-        return paged_attention_tiled(q, k_cache, v_cache, block_table, step.cu_q, step.q_pos0,
-                                     window, scale)
-    return paged_attention_generic(q, k_cache, v_cache, block_table, step.seq_of_token,
-                                   step.positions, window, scale)
+    return _paged_attention_softcap(q, k_cache, v_cache, block_table, step, window, scale, 0.0)
+
+
+def paged_attention_decode_any(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                               block_table: torch.Tensor, kv_len: torch.Tensor, max_kv_len: int,
+                               window: int, scale: float, softcap: float = 0.0,
+                               splits: Optional[int] = None):
+    """Split-KV attention in fp32 arithmetic for a batch in which sequence s brings the one
+    query q[s] at position kv_len[s] - 1: any head size up to 512, value heads of a size
+    of their own, any element type.  Returns [S, heads, value size]."""
+    _chk("q", q)
+    _chk("k_cache", k_cache, q.dtype)
+    _chk("v_cache", v_cache, q.dtype)
+    _chk("block_table", block_table, torch.int32)
+    _chk("kv_len", kv_len, torch.int32)
+    S, heads, hd = q.shape
+    P, kvh, page, chd = k_cache.shape
+    vd = v_cache.shape[3]
+    if chd != hd or v_cache.shape[:3] != k_cache.shape[:3]:
+        raise KernelError("paged_attention_decode_any: cache geometry differs from the query's")
+    if kv_len.numel() != S or block_table.shape[0] != S:
+        raise KernelError("paged_attention_decode_any: one query per sequence is required")
+    lib = _lib()
+    if splits is None:
+        splits = lib.ix_attn_decode_any_splits(S, heads, kvh, hd, vd, int(max_kv_len))
+    out = torch.empty((S, heads, vd), dtype=q.dtype, device=q.device)
+    part_o = part_ml = None
+    if splits > 1:
+        part_o = torch.empty((S, heads, splits, vd), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((S, heads, splits, 2), dtype=torch.float32, device=q.device)
+    _check(lib.ix_paged_attention_decode_any(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(kv_len), _ptr(part_o),
+        _ptr(part_ml), _ptr(out), _dtype_code(q), S, heads, kvh, hd, vd, page,
+        block_table.shape[1], window, ctypes.c_float(scale), ctypes.c_float(softcap), splits,
+        _stream()), "paged_attention_decode_any")
+    _count(2 if splits > 1 else 1)
+    return out
+
+
+# From this many keys on a step of single tokens goes to the split-KV form of the
+# fp32-arithmetic kernels; below it a block per (token, head) walks them as fast.
+DECODE_ANY_MIN_KEYS = 128
 
 
 def _paged_attention_softcap(q, k_cache, v_cache, block_table, step, window, scale, softcap):
     """The fp32-arithmetic kernels (squashed scores or not)."""
     hd = q.shape[2]
+    if (getattr(step, "all_decode", False) and getattr(step, "kv_len", None) is not None
+            and step.num_tokens == step.num_seqs and step.max_kv_len >= DECODE_ANY_MIN_KEYS
+            and max(hd, v_cache.shape[3]) <= 512):
+        return paged_attention_decode_any(q, k_cache, v_cache, block_table, step.kv_len,
+                                          step.max_kv_len, window, scale, softcap)
     if (step.num_tokens >= TILED_ATTENTION_MIN_QUERIES * step.num_seqs
             and _lib().ix_paged_attention_tiled_applies(hd)
             and _lib().ix_paged_attention_tiled_applies(v_cache.shape[3])
@@ -1707,13 +1747,19 @@ def delta_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta_raw
             decay.shape != (T, heads * dim) or tuple(state.shape[1:]) != (heads, dim, vdim):
         raise KernelError("delta_recurrence: inputs and state do not fit together")
     out = torch.empty((T, heads, vdim), dtype=torch.float32, device=q.device)
+    seg_len, nseg = recurrence_segments(int(getattr(step, "max_q_len", 0) or T), step.num_seqs,
+                                        heads, vdim + dim)
+    scratch = None
+    if nseg > 1:
+        scratch = torch.empty((_lib().ix_delta_recurrence_scratch_floats(
+            step.num_seqs, heads, dim, vdim, nseg),), dtype=torch.float32, device=q.device)
     _check(_lib().ix_delta_recurrence(
         _ptr(q), ctypes.c_longlong(ldq), _ptr(k), ctypes.c_longlong(ldk), _ptr(v),
         ctypes.c_longlong(ldv), _ptr(beta_raw), ctypes.c_longlong(ldb), _dtype_code(q),
         _ptr(decay), _ptr(state), _ptr(step.cu_q), _ptr(step.state_slot), _ptr(out),
         step.num_seqs, heads, kv_heads, dim, vdim, ctypes.c_float(unit_eps),
-        ctypes.c_float(q_scale), _stream()), "delta_recurrence")
-    _count()
+        ctypes.c_float(q_scale), seg_len, nseg, _ptr(scratch), _stream()), "delta_recurrence")
+    _count(2 if nseg > 1 else 1)
     return out
 
 

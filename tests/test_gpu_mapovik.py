@@ -230,6 +230,42 @@ def test_delta_recurrence(dtype, H, HK, K, V):
     assert torch.equal(st.cpu()[3], state[3])
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,HK,K,V", [(2, 1, 24, 40), (4, 2, 64, 128), (3, 3, 5, 7), (2, 2, 128, 32),
+                                      (1, 1, 40, 33)])
+def test_delta_recurrence_in_segments(dtype, H, HK, K, V):
+    """Long prompts are walked in segments whose start states are rebuilt from each earlier
+    segment's own state and the product of its transition matrices: a long prompt beside a
+    single token and a portion that continues a state, against the plain walk and against
+    the same tokens in portions too short to be cut."""
+    g = torch.Generator().manual_seed(H * K + V)
+    q_lens = [700, 1, 131]
+    step = _step(q_lens, [0, 40, 64], slots=[2, 0, 1])
+    T = sum(q_lens)
+    q, k = (torch.randn(T, HK * K, generator=g).to(dtype) for _ in range(2))
+    v = torch.randn(T, H * V, generator=g).to(dtype)
+    beta = (torch.randn(T, H, generator=g) * 2).to(dtype)
+    decay = torch.rand(T, H * K, generator=g) * 0.1 + 0.9      # far tokens stay in the state
+    state = torch.randn(3, H, K, V, generator=g)
+    st_ref = state.clone()
+    ref = host_ops.delta_recurrence(q, k, v, beta, decay, st_ref, step, H, HK, K, V, 1e-6,
+                                    K ** -0.5)
+    st = state.cuda()
+    args = lambda sl: [t[sl].cuda() for t in (q, k, v, beta, decay)]
+    out = _ops().delta_recurrence(*args(slice(0, T)), st, _cuda(step), H, HK, K, V, 1e-6,
+                                  K ** -0.5)
+    assert _rel(out.cpu(), ref) <= 5e-5 and _rel(st.cpu(), st_ref) <= 5e-5
+    st2, at, outs = state.cuda(), 0, []
+    while at < 700:
+        n = min(100, 700 - at)
+        outs.append(_ops().delta_recurrence(*args(slice(at, at + n)), st2,
+                                            _cuda(_step([n], [at], [2])), H, HK, K, V, 1e-6,
+                                            K ** -0.5))
+        at += n
+    assert _rel(torch.cat(outs).cpu(), out[:700].cpu()) <= 2e-5
+    assert _rel(st2[2].cpu(), st[2].cpu()) <= 2e-5
+
+
 def test_recurrences_do_not_depend_on_the_cut():
     """The same tokens in one step, in portions and one by one, alone and beside another
     sequence: the same bits, in the outputs and in the states."""
@@ -296,7 +332,10 @@ def test_delta_state_keeps_one_write_from_far_back(far):
             at += n
         outs.append(last[-1].cpu())
         torch.testing.assert_close(last[-1].cpu(), torch.full((H, V), 5.0), rtol=1e-4, atol=1e-4)
-    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    if T < 128:
+        assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    else:      # long portions are walked in segments: the same up to rounding
+        assert _rel(outs[1], outs[0]) <= 1e-6 and _rel(outs[2], outs[0]) <= 1e-6
     # a decay of one half per token on the written channel takes the value away
     decay[:, 0] = 0.5
     st = torch.zeros(1, H, K, V, device="cuda")
@@ -434,6 +473,32 @@ def test_attention_with_values_of_their_own_size_finds_one_key(dtype, D, VD, dec
         if not decode and key_pos == 700:
             # the query before it must not see that key
             assert float(out[n0 - 2].abs().mean()) < 1.0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,G,D,VD", [(3, 1, 24, 40), (10, 2, 96, 160), (8, 8, 200, 72),
+                                      (2, 1, 320, 512), (16, 2, 64, 64), (6, 2, 7, 5)])
+@pytest.mark.parametrize("window,softcap", [(0, 0.0), (100, 0.0), (0, 3.0)])
+def test_single_token_attention_of_any_size_in_splits(dtype, H, G, D, VD, window, softcap):
+    """Steps of single tokens over contexts of 1 to 1,000 keys: every grouping of heads,
+    sizes on both sides of a lane's share, the split chosen by the kernel, none and one
+    that leaves blocks without keys."""
+    page, scale = 8, 0.4
+    q_lens, starts = [1, 1, 1, 1], [0, 129, 999, 63]
+    step, bt, kc, vc, q = _kv_case(H + D, H, G, D, VD, page, q_lens, starts, dtype)
+    ref = host_ops.paged_attention_generic(q, kc, vc, bt, step.seq_of_token, step.positions,
+                                           window, scale, softcap).float()
+    cs = _cuda(step)
+    for splits in (None, 1, 40):
+        out = _ops().paged_attention_decode_any(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(),
+                                                cs.kv_len, cs.max_kv_len, window, scale, softcap,
+                                                splits=splits).cpu().float()
+        assert out.shape == (4, H, VD)
+        torch.testing.assert_close(out, ref, **_tol(dtype))
+    # the dispatcher takes this kernel for such a step
+    via = _ops().paged_attention(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), cs, window, scale,
+                                 softcap=softcap, fp32_weights=True).cpu().float()
+    torch.testing.assert_close(via, ref, **_tol(dtype))
 
 
 # -- the engine against the plain model ------------------------------------------------
