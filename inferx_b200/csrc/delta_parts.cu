@@ -469,11 +469,24 @@ delta_recurrence_kernel(const TA* __restrict__ q, long long ldq, const TA* __res
         const int kk = kk0 + i;
         acc[i] = (kk < K && col_ok) ? my_s[((size_t)e * K + kk) * V + col] : 0.f;
       }
-      for (int jj = 0; jj < K; ++jj) {
-        const float x = x_s[jj * RC_COLS + lane];
+      if ((K & 3) == 0) {                   // four entries of a row per load, same order of sums
+        for (int jj = 0; jj < K; jj += 4) {
+          const float x0 = x_s[jj * RC_COLS + lane], x1 = x_s[(jj + 1) * RC_COLS + lane];
+          const float x2 = x_s[(jj + 2) * RC_COLS + lane], x3 = x_s[(jj + 3) * RC_COLS + lane];
 #pragma unroll
-        for (int i = 0; i < KPT; ++i)
-          if (kk0 + i < K) acc[i] = fmaf(A[(size_t)(kk0 + i) * K + jj], x, acc[i]);
+          for (int i = 0; i < KPT; ++i)
+            if (kk0 + i < K) {
+              const float4 a = *reinterpret_cast<const float4*>(A + (size_t)(kk0 + i) * K + jj);
+              acc[i] = fmaf(a.w, x3, fmaf(a.z, x2, fmaf(a.y, x1, fmaf(a.x, x0, acc[i]))));
+            }
+        }
+      } else {
+        for (int jj = 0; jj < K; ++jj) {
+          const float x = x_s[jj * RC_COLS + lane];
+#pragma unroll
+          for (int i = 0; i < KPT; ++i)
+            if (kk0 + i < K) acc[i] = fmaf(A[(size_t)(kk0 + i) * K + jj], x, acc[i]);
+        }
       }
       __syncthreads();
 #pragma unroll
@@ -491,14 +504,23 @@ delta_recurrence_kernel(const TA* __restrict__ q, long long ldq, const TA* __res
     }
   }
   int buf = 0;
+  const int st_c = threadIdx.x / K, st_k = threadIdx.x % K;
+  const int step_c = blockDim.x / K, step_k = blockDim.x % K;
   for (int t0 = t_begin; t0 < t_end; t0 += RC_CHUNK) {
     const int n = min(RC_CHUNK, t_end - t0);
-    for (int i = threadIdx.x; i < n * K; i += blockDim.x) {
-      const int c = i / K, kk = i - c * K;
+    // thread i takes entries i, i + blockDim.x, ... of the chunk's [n][K]; its (token, entry)
+    // advances by a fixed step, so no division runs per entry
+    for (int c = st_c, kk = st_k; c < n;) {
       const size_t t = (size_t)(t0 + c);
       if (MODE != RC_LOCAL) q_s[c * KP + kk] = to_f32(q[t * ldq + (size_t)j * K + kk]);
       k_s[c * KP + kk] = to_f32(k[t * ldk + (size_t)j * K + kk]);
       g_s[c * KP + kk] = decay[(t * H + h) * K + kk];
+      c += step_c;
+      kk += step_k;
+      if (kk >= K) {
+        kk -= K;
+        ++c;
+      }
     }
     for (int i = threadIdx.x; i < n * RC_COLS; i += blockDim.x) {
       const int c = i / RC_COLS, jj = i - c * RC_COLS;
@@ -654,6 +676,65 @@ IX_API int ix_ssd_recurrence(const void* xbc, long long ld, const void* dt_raw, 
 #undef SSD_GO
 #undef SSD_ONE
   return ix_launch_status();
+}
+
+template <typename TA, int KPT>
+static int dr_resident(int mode, size_t smem, int threads) {
+  int n = 0;
+  if (mode == RC_LOCAL) {
+    auto kern = delta_recurrence_kernel<TA, KPT, RC_LOCAL>;
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, threads, smem);
+  } else {
+    auto kern = delta_recurrence_kernel<TA, KPT, RC_JOINED>;
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, threads, smem);
+  }
+  return n;
+}
+
+// Segments for a step whose longest sequence brings max_q_len tokens: as many as keep each
+// of the two passes within the blocks the device holds at once (a second, nearly empty
+// round of blocks would double a pass), none shorter than 64 tokens.  Returns the number
+// of segments and sets *seg_len; 1 and 0 when the sequences are walked from end to end.
+IX_API int ix_delta_recurrence_segments(int dtype, int S, int H, int K, int V, int max_q_len,
+                                        int min_tokens, int max_segments, int* seg_len) {
+  *seg_len = 0;
+  if (S <= 0 || H <= 0 || K <= 0 || V <= 0 || K > 8 * 64 || max_q_len < min_tokens) return 1;
+  const int KS = rc_slices(K);
+  const int kpt = (K + KS - 1) / KS;
+  const int KPT = kpt <= 8 ? 8 : kpt <= 16 ? 16 : kpt <= 32 ? 32 : 64;
+  const size_t smem = ((size_t)3 * RC_CHUNK * KS * KPT + RC_CHUNK * RC_COLS + 2 * RC_CHUNK +
+                       (size_t)2 * KS * 2 * RC_COLS) * sizeof(float);
+  int dev = 0, sms = 0, local = 0, joined = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+#define DR_OCC(KK)                                                                           \
+  IX_DISPATCH_DTYPE(dtype, TA, {                                                             \
+    local = dr_resident<TA, KK>(RC_LOCAL, smem, RC_COLS * KS);                               \
+    joined = dr_resident<TA, KK>(RC_JOINED, smem, RC_COLS * KS);                             \
+  })
+  if (KPT == 8) DR_OCC(8);
+  else if (KPT == 16) DR_OCC(16);
+  else if (KPT == 32) DR_OCC(32);
+  else DR_OCC(64);
+#undef DR_OCC
+  const long long vtiles = (V + RC_COLS - 1) / RC_COLS, atiles = (K + RC_COLS - 1) / RC_COLS;
+  const long long per_joined = (long long)S * H * vtiles;
+  const long long per_local = (long long)S * H * (vtiles + atiles);
+  long long want = (long long)joined * sms / per_joined;
+  if ((long long)local * sms / per_local < want) want = (long long)local * sms / per_local;
+  if (want > max_segments) want = max_segments;
+  if (want < 2) return 1;
+  int len = (int)((max_q_len + want - 1) / want);
+  len = (len + RC_CHUNK - 1) / RC_CHUNK * RC_CHUNK;
+  if (len < 64) len = 64;
+  const int nseg = (max_q_len + len - 1) / len;
+  if (nseg <= 1) return 1;
+  *seg_len = len;
+  return nseg;
 }
 
 // Floats of scratch the segmented delta walk needs.

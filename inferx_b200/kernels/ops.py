@@ -1747,8 +1747,15 @@ def delta_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta_raw
             decay.shape != (T, heads * dim) or tuple(state.shape[1:]) != (heads, dim, vdim):
         raise KernelError("delta_recurrence: inputs and state do not fit together")
     out = torch.empty((T, heads, vdim), dtype=torch.float32, device=q.device)
-    seg_len, nseg = recurrence_segments(int(getattr(step, "max_q_len", 0) or T), step.num_seqs,
-                                        heads, vdim + dim)
+    # the kernel's side knows how many of its blocks the device holds at once
+    seg = ctypes.c_int(0)
+    nseg = _lib().ix_delta_recurrence_segments(
+        _dtype_code(q), step.num_seqs, heads, dim, vdim,
+        int(getattr(step, "max_q_len", 0) or T), RECURRENCE_SEGMENT_MIN, RECURRENCE_MAX_SEGMENTS,
+        ctypes.byref(seg))
+    if nseg < 1:
+        _check(nseg, "delta_recurrence_segments")
+    seg_len = seg.value
     scratch = None
     if nseg > 1:
         scratch = torch.empty((_lib().ix_delta_recurrence_scratch_floats(
