@@ -21,6 +21,70 @@
 // add + norm.  One block per output row; the row is kept in shared memory between the
 // passes (mean, then the mean of squared deviations, then the output).
 // ---------------------------------------------------------------------------
+// four neighbouring entries at once (the address is a multiple of four entries)
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 ld4(const bf16* p) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x);
+  const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+  return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+__device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void st4(bf16* p, float4 v) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 u;
+  u.x = *reinterpret_cast<const unsigned*>(&a);
+  u.y = *reinterpret_cast<const unsigned*>(&b);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+
+// The same passes with four entries per access, for rows of a multiple of four entries on
+// 16-byte boundaries.  A thread's partial sums run over other entries than in the form
+// below: the two differ by rounding, and one row size always takes the same form.
+template <typename TD, typename TO>
+__global__ void add_scaled_norm_vec_kernel(float* __restrict__ resid,
+                                           const TD* __restrict__ delta, float scale,
+                                           const float* __restrict__ vector,
+                                           const float* __restrict__ gain,
+                                           const int* __restrict__ rows, TO* __restrict__ out,
+                                           int H, float eps, int center, int write_back) {
+  extern __shared__ __align__(16) float row_s[];   // [H] + 32
+  float* scratch = row_s + H;
+  IX_PDL_WAIT();
+  const int r = blockIdx.x;
+  const size_t src = rows ? (size_t)rows[r] : (size_t)r;
+  float* x = resid + src * H;
+  float sum = 0.f;
+  for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+    float4 v = ld4(x + i);
+    if (delta) {
+      const float4 d = ld4(delta + src * H + i);
+      v.x += scale * d.x, v.y += scale * d.y, v.z += scale * d.z, v.w += scale * d.w;
+    }
+    if (vector) {
+      const float4 a = ld4(vector + i);
+      v.x += a.x, v.y += a.y, v.z += a.z, v.w += a.w;
+    }
+    st4(row_s + i, v);
+    if (write_back) st4(x + i, v);
+    sum += (v.x + v.y) + (v.z + v.w);
+  }
+  float mean = 0.f;
+  if (center) mean = block_sum(sum, scratch) / (float)H;
+  float sq = 0.f;
+  for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {   // a thread's own entries
+    const float4 v = ld4(row_s + i);
+    const float a = v.x - mean, b = v.y - mean, c = v.z - mean, d = v.w - mean;
+    sq += (a * a + b * b) + (c * c + d * d);
+  }
+  const float inv = 1.0f / sqrtf(block_sum(sq, scratch) / (float)H + eps);
+  for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+    const float4 v = ld4(row_s + i), g = ld4(gain + i);
+    st4(out + (size_t)r * H + i, make_float4((v.x - mean) * inv * g.x, (v.y - mean) * inv * g.y,
+                                             (v.z - mean) * inv * g.z, (v.w - mean) * inv * g.w));
+  }
+}
+
 template <typename TD, typename TO>
 __global__ void add_scaled_norm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
                                        float scale, const float* __restrict__ vector,
@@ -63,10 +127,14 @@ IX_API int ix_add_scaled_norm(float* resid, const void* delta, int delta_dtype, 
   if (H <= 0) return IX_ERR_SIZE;
   const size_t smem = (size_t)(H + 32) * sizeof(float);
   if (smem > 200 * 1024) return IX_ERR_SMEM;
-  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+  const auto at16 = [](const void* p) { return p == nullptr || ((uintptr_t)p & 15) == 0; };
+  const bool vec = H % 4 == 0 && at16(resid) && at16(delta) && at16(vector) && at16(gain) &&
+                   at16(out);
+  const int threads = vec ? (H >= 4096 ? 512 : (H >= 1024 ? 256 : 128))
+                          : (H >= 2048 ? 512 : (H >= 512 ? 256 : 128));
 #define IX_ASN(TD, TO)                                                                       \
   do {                                                                                       \
-    auto kern = add_scaled_norm_kernel<TD, TO>;                                              \
+    auto kern = vec ? add_scaled_norm_vec_kernel<TD, TO> : add_scaled_norm_kernel<TD, TO>;   \
     if (smem > 48 * 1024)                                                                    \
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
     ix_launch(kern, dim3(R), dim3(threads), smem, stream, resid, (const TD*)delta, scale,    \
@@ -173,6 +241,86 @@ __global__ void causal_conv_kernel(const TA* __restrict__ x, long long ldx,
   out[(size_t)t * C + c] = from_f32<TA>(acc);
 }
 
+// The same sums for long steps: a thread owns two neighbouring channels of CONV_RUN tokens in
+// a row and keeps the last TAPS - 1 inputs in registers, so that an input is read once.  The
+// window is filled as above at the run's first token and wherever a sequence begins inside
+// the run; the sum of a token runs over the same terms in the same order as above, so the
+// two kernels give the same bits.
+#define CONV_RUN 16
+template <typename TA, int TAPS>
+__global__ void __launch_bounds__(CONV_THREADS)
+causal_conv_run_kernel(const TA* __restrict__ x, long long ldx, const float* __restrict__ w,
+                       const float* __restrict__ bias, const float* __restrict__ state,
+                       const int* __restrict__ cu_q, const int* __restrict__ seq_of_token,
+                       const int* __restrict__ state_slot, TA* __restrict__ out, int T, int C,
+                       int act) {
+  IX_PDL_WAIT();
+  const int t0 = blockIdx.x * CONV_RUN;
+  const int c = (blockIdx.y * CONV_THREADS + threadIdx.x) * 2;
+  if (c >= C) return;
+  float wv[2][TAPS], win[2][TAPS > 1 ? TAPS - 1 : 1];
+#pragma unroll
+  for (int j = 0; j < TAPS; ++j) {
+    wv[0][j] = w[(size_t)c * TAPS + j];
+    wv[1][j] = w[(size_t)(c + 1) * TAPS + j];
+  }
+  const float b0 = bias ? bias[c] : 0.f, b1 = bias ? bias[c + 1] : 0.f;
+  const int t1 = min(T, t0 + CONV_RUN);
+  for (int t = t0; t < t1; ++t) {
+    const int s = seq_of_token[t];
+    const int begin = cu_q[s];
+    if (t == t0 || t == begin) {
+      const float* st = state + (size_t)state_slot[s] * (TAPS - 1) * C;
+#pragma unroll
+      for (int j = 0; j < TAPS - 1; ++j) {
+        const int src = t - (TAPS - 1) + j;
+        if (src >= begin) {
+          win[0][j] = to_f32(x[(size_t)src * ldx + c]);
+          win[1][j] = to_f32(x[(size_t)src * ldx + c + 1]);
+        } else {
+          const int back = begin - src;
+          win[0][j] = st[(size_t)(TAPS - 1 - back) * C + c];
+          win[1][j] = st[(size_t)(TAPS - 1 - back) * C + c + 1];
+        }
+      }
+    }
+    float cur0, cur1;
+    if (sizeof(TA) == 2) {
+      const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(x + (size_t)t * ldx + c);
+      cur0 = __low2float(v), cur1 = __high2float(v);
+    } else {
+      const float2 v = *reinterpret_cast<const float2*>(x + (size_t)t * ldx + c);
+      cur0 = v.x, cur1 = v.y;
+    }
+    float a0 = b0, a1 = b1;
+#pragma unroll
+    for (int j = 0; j < TAPS - 1; ++j) {
+      a0 = fmaf(wv[0][j], win[0][j], a0);
+      a1 = fmaf(wv[1][j], win[1][j], a1);
+    }
+    a0 = fmaf(wv[0][TAPS - 1], cur0, a0);
+    a1 = fmaf(wv[1][TAPS - 1], cur1, a1);
+#pragma unroll
+    for (int j = 0; j + 1 < TAPS - 1; ++j) {
+      win[0][j] = win[0][j + 1];
+      win[1][j] = win[1][j + 1];
+    }
+    if (TAPS > 1) {
+      win[0][TAPS - 2] = cur0;
+      win[1][TAPS - 2] = cur1;
+    }
+    if (act) {
+      a0 = a0 / (1.0f + expf(-a0));
+      a1 = a1 / (1.0f + expf(-a1));
+    }
+    out[(size_t)t * C + c] = from_f32<TA>(a0);
+    out[(size_t)t * C + c + 1] = from_f32<TA>(a1);
+  }
+}
+
+// Steps of this many tokens or more take the kernel that walks runs of tokens.
+#define CONV_RUN_MIN_TOKENS 1024
+
 // The state moves on: entry i becomes the input taps-1-i tokens before the sequence's
 // next token.  A thread owns one channel of one sequence and walks i upwards; what it
 // reads from the old state lies above what it has written.
@@ -203,14 +351,27 @@ IX_API int ix_causal_conv(const void* x, int dtype, long long ldx, const float* 
   if (C <= 0 || taps < 1 || taps > CONV_MAX_TAPS || ldx < C) return IX_ERR_SIZE;
   const int cb = (C + CONV_THREADS - 1) / CONV_THREADS;
   if (cb > 65535) return IX_ERR_SIZE;
+  const size_t two = dtype == IX_F32 ? 8 : 4;
+  const bool run = T >= CONV_RUN_MIN_TOKENS && taps >= 2 && taps <= 4 && C % 2 == 0 &&
+                   ldx % 2 == 0 && (uintptr_t)x % two == 0 && (uintptr_t)out % two == 0;
+  const dim3 rgrid((T + CONV_RUN - 1) / CONV_RUN, (C / 2 + CONV_THREADS - 1) / CONV_THREADS);
+#define CONV_GO(TAPS)                                                                        \
+  ix_launch(causal_conv_run_kernel<TA, TAPS>, rgrid, dim3(CONV_THREADS), 0, stream,          \
+            (const TA*)x, ldx, w, bias, (const float*)state, cu_q, seq_of_token, state_slot, \
+            (TA*)out, T, C, act)
   IX_DISPATCH_DTYPE(dtype, TA, {
-    ix_launch(causal_conv_kernel<TA>, dim3(T, cb), dim3(CONV_THREADS), 0, stream, (const TA*)x,
-              ldx, w, bias, (const float*)state, cu_q, seq_of_token, state_slot, (TA*)out, C,
-              taps, act);
+    if (run && taps == 2) CONV_GO(2);
+    else if (run && taps == 3) CONV_GO(3);
+    else if (run && taps == 4) CONV_GO(4);
+    else
+      ix_launch(causal_conv_kernel<TA>, dim3(T, cb), dim3(CONV_THREADS), 0, stream,
+                (const TA*)x, ldx, w, bias, (const float*)state, cu_q, seq_of_token,
+                state_slot, (TA*)out, C, taps, act);
     if (taps > 1)
       ix_launch(conv_state_update_kernel<TA>, dim3(S, cb), dim3(CONV_THREADS), 0, stream,
                 (const TA*)x, ldx, state, cu_q, state_slot, C, taps);
   });
+#undef CONV_GO
   return ix_launch_status();
 }
 

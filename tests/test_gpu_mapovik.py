@@ -154,6 +154,42 @@ def test_causal_conv_does_not_depend_on_the_cut():
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("C,taps,bias", [(64, 4, True), (38, 2, False), (258, 3, True)])
+def test_causal_conv_of_long_steps_walks_runs_of_tokens(dtype, C, taps, bias):
+    """Steps of a thousand tokens and more: sequences that begin inside a run of tokens, at
+    its first and at its last token, a sequence of one token, kept inputs from earlier; the
+    same bits as the same tokens in short steps."""
+    g = torch.Generator().manual_seed(C * taps)
+    q_lens = [16, 1000, 1, 15, 2, 331]
+    starts = [0, 7, 3, 0, 1, 40]
+    step = _step(q_lens, starts, slots=[5, 0, 2, 4, 1, 6])
+    T = sum(q_lens)
+    wide = torch.randn(T, C + 6, generator=g).to(dtype)
+    w = torch.randn(C, taps, generator=g)
+    b = torch.randn(C, generator=g) if bias else None
+    state = torch.randn(7, taps - 1, C, generator=g)
+    st_ref = state.clone()
+    ref = host_ops.causal_conv(wide[:, 2:2 + C], w, b, st_ref, step, silu=True)
+    st = state.cuda()
+    bc = None if b is None else b.cuda()
+    out = _ops().causal_conv(wide.cuda()[:, 2:2 + C], w.cuda(), bc, st, _cuda(step), silu=True)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), **_tol(dtype))
+    torch.testing.assert_close(st.cpu(), st_ref, rtol=1e-6, atol=1e-6)
+    # sequence by sequence in portions of at most 300 tokens (the kernel of single tokens)
+    st2, at, parts = state.cuda(), 0, []
+    for n_all, p0, slot in zip(q_lens, starts, [5, 0, 2, 4, 1, 6]):
+        done = 0
+        while done < n_all:
+            n = min(300, n_all - done)
+            xx = wide.cuda()[at + done:at + done + n, 2:2 + C]
+            parts.append(_ops().causal_conv(xx, w.cuda(), bc, st2,
+                                            _cuda(_step([n], [p0 + done], [slot])), silu=True))
+            done += n
+        at += n_all
+    assert torch.equal(torch.cat(parts), out) and torch.equal(st2, st)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,V,N,G", [(4, 24, 32, 2), (3, 8, 12, 1), (5, 3, 7, 5), (2, 64, 128, 1),
                                      (8, 40, 64, 4), (1, 100, 16, 1)])
 def test_state_space_recurrence(dtype, H, V, N, G):
