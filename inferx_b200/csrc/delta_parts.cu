@@ -247,6 +247,14 @@ __global__ void causal_conv_kernel(const TA* __restrict__ x, long long ldx,
 // the run; the sum of a token runs over the same terms in the same order as above, so the
 // two kernels give the same bits.
 #define CONV_RUN 16
+template <typename TA> struct ConvPair;
+template <> struct ConvPair<float> { typedef float2 type; };
+template <> struct ConvPair<bf16> { typedef __nv_bfloat162 type; };
+__device__ __forceinline__ float2 pair_f32(float2 v) { return v; }
+__device__ __forceinline__ float2 pair_f32(__nv_bfloat162 v) {
+  return make_float2(__low2float(v), __high2float(v));
+}
+
 template <typename TA, int TAPS>
 __global__ void __launch_bounds__(CONV_THREADS)
 causal_conv_run_kernel(const TA* __restrict__ x, long long ldx, const float* __restrict__ w,
@@ -265,8 +273,16 @@ causal_conv_run_kernel(const TA* __restrict__ x, long long ldx, const float* __r
     wv[1][j] = w[(size_t)(c + 1) * TAPS + j];
   }
   const float b0 = bias ? bias[c] : 0.f, b1 = bias ? bias[c + 1] : 0.f;
-  const int t1 = min(T, t0 + CONV_RUN);
-  for (int t = t0; t < t1; ++t) {
+  // the run's inputs are all on their way before the first is used
+  typedef typename ConvPair<TA>::type P2;
+  P2 raw[CONV_RUN];
+#pragma unroll
+  for (int i = 0; i < CONV_RUN; ++i)
+    if (t0 + i < T) raw[i] = *reinterpret_cast<const P2*>(x + (size_t)(t0 + i) * ldx + c);
+#pragma unroll
+  for (int i = 0; i < CONV_RUN; ++i) {
+    const int t = t0 + i;
+    if (t >= T) break;
     const int s = seq_of_token[t];
     const int begin = cu_q[s];
     if (t == t0 || t == begin) {
@@ -284,14 +300,8 @@ causal_conv_run_kernel(const TA* __restrict__ x, long long ldx, const float* __r
         }
       }
     }
-    float cur0, cur1;
-    if (sizeof(TA) == 2) {
-      const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(x + (size_t)t * ldx + c);
-      cur0 = __low2float(v), cur1 = __high2float(v);
-    } else {
-      const float2 v = *reinterpret_cast<const float2*>(x + (size_t)t * ldx + c);
-      cur0 = v.x, cur1 = v.y;
-    }
+    const float2 cur = pair_f32(raw[i]);
+    const float cur0 = cur.x, cur1 = cur.y;
     float a0 = b0, a1 = b1;
 #pragma unroll
     for (int j = 0; j < TAPS - 1; ++j) {
@@ -313,8 +323,11 @@ causal_conv_run_kernel(const TA* __restrict__ x, long long ldx, const float* __r
       a0 = a0 / (1.0f + expf(-a0));
       a1 = a1 / (1.0f + expf(-a1));
     }
-    out[(size_t)t * C + c] = from_f32<TA>(a0);
-    out[(size_t)t * C + c + 1] = from_f32<TA>(a1);
+    if (sizeof(TA) == 2) {
+      *reinterpret_cast<__nv_bfloat162*>(out + (size_t)t * C + c) = __floats2bfloat162_rn(a0, a1);
+    } else {
+      *reinterpret_cast<float2*>(out + (size_t)t * C + c) = make_float2(a0, a1);
+    }
   }
 }
 
@@ -983,16 +996,54 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, const TA* _
   }
 }
 
+// four entries per access (groups of a multiple of four entries, rows on such boundaries);
+// against the form above a thread's partial sums run over other entries
+template <typename TA>
+__global__ void gated_group_norm_vec_kernel(const float* __restrict__ y,
+                                            const TA* __restrict__ z, long long ldz,
+                                            const float* __restrict__ gain,
+                                            TA* __restrict__ out, int W, int groups, float eps) {
+  __shared__ float scratch[32];
+  IX_PDL_WAIT();
+  const int t = blockIdx.x, g = blockIdx.y;
+  const int n = W / groups, c0 = g * n;
+  const float* yr = y + (size_t)t * W + c0;
+  const TA* zr = z + (size_t)t * ldz + c0;
+  float sq = 0.f;
+  for (int i = threadIdx.x * 4; i < n; i += blockDim.x * 4) {
+    const float4 zz = ld4(zr + i), yy = ld4(yr + i);
+    const float a = yy.x * (zz.x / (1.0f + expf(-zz.x))), b = yy.y * (zz.y / (1.0f + expf(-zz.y)));
+    const float c = yy.z * (zz.z / (1.0f + expf(-zz.z))), d = yy.w * (zz.w / (1.0f + expf(-zz.w)));
+    sq += (a * a + b * b) + (c * c + d * d);
+  }
+  const float inv = 1.0f / sqrtf(block_sum(sq, scratch) / (float)n + eps);
+  for (int i = threadIdx.x * 4; i < n; i += blockDim.x * 4) {
+    const float4 zz = ld4(zr + i), yy = ld4(yr + i), gg = ld4(gain + c0 + i);
+    const float a = yy.x * (zz.x / (1.0f + expf(-zz.x))), b = yy.y * (zz.y / (1.0f + expf(-zz.y)));
+    const float c = yy.z * (zz.z / (1.0f + expf(-zz.z))), d = yy.w * (zz.w / (1.0f + expf(-zz.w)));
+    st4(out + (size_t)t * W + c0 + i,
+        make_float4(a * inv * gg.x, b * inv * gg.y, c * inv * gg.z, d * inv * gg.w));
+  }
+}
+
+static inline bool at_four(const void* p, size_t elem) { return ((uintptr_t)p % (4 * elem)) == 0; }
+
 IX_API int ix_gated_group_norm(const float* y, const void* z, int dtype, long long ldz,
                                const float* gain, void* out, int T, int W, int groups, float eps,
                                cudaStream_t stream) {
   if (T <= 0) return IX_OK;
   if (W <= 0 || groups <= 0 || W % groups || ldz < W || groups > 65535) return IX_ERR_SIZE;
   const int n = W / groups;
-  const int threads = n >= 1024 ? 256 : (n >= 256 ? 128 : 64);
-  IX_DISPATCH_DTYPE(dtype, TA,
-                    ix_launch(gated_group_norm_kernel<TA>, dim3(T, groups), dim3(threads), 0,
-                              stream, y, (const TA*)z, ldz, gain, (TA*)out, W, groups, eps));
+  const size_t el = dtype == IX_F32 ? 4 : 2;
+  const bool vec = n % 4 == 0 && ldz % 4 == 0 && at_four(y, 4) && at_four(gain, 4) &&
+                   at_four(z, el) && at_four(out, el);
+  const int threads = vec ? (n >= 2048 ? 256 : (n >= 512 ? 128 : 64))
+                          : (n >= 1024 ? 256 : (n >= 256 ? 128 : 64));
+  IX_DISPATCH_DTYPE(dtype, TA, {
+    auto kern = vec ? gated_group_norm_vec_kernel<TA> : gated_group_norm_kernel<TA>;
+    ix_launch(kern, dim3(T, groups), dim3(threads), 0, stream, y, (const TA*)z, ldz, gain,
+              (TA*)out, W, groups, eps);
+  });
   return ix_launch_status();
 }
 
@@ -1021,15 +1072,49 @@ __global__ void normed_pair_mean_kernel(const TL* __restrict__ l, const TL* __re
     out[(size_t)t * W + i] = 0.5f * (to_f32(lr[i]) * il * gl[i] + to_f32(rr[i]) * ir * gr[i]);
 }
 
+template <typename TL>
+__global__ void normed_pair_mean_vec_kernel(const TL* __restrict__ l, const TL* __restrict__ r,
+                                            const float* __restrict__ gl,
+                                            const float* __restrict__ gr,
+                                            float* __restrict__ out, int W, float eps) {
+  __shared__ float scratch[32];
+  IX_PDL_WAIT();
+  const int t = blockIdx.x;
+  const TL* lr = l + (size_t)t * W;
+  const TL* rr = r + (size_t)t * W;
+  float sl = 0.f, sr = 0.f;
+  for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {
+    const float4 a = ld4(lr + i), b = ld4(rr + i);
+    sl += (a.x * a.x + a.y * a.y) + (a.z * a.z + a.w * a.w);
+    sr += (b.x * b.x + b.y * b.y) + (b.z * b.z + b.w * b.w);
+  }
+  const float il = 1.0f / sqrtf(block_sum(sl, scratch) / (float)W + eps);
+  const float ir = 1.0f / sqrtf(block_sum(sr, scratch) / (float)W + eps);
+  for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {
+    const float4 a = ld4(lr + i), b = ld4(rr + i), ga = ld4(gl + i), gb = ld4(gr + i);
+    st4(out + (size_t)t * W + i,
+        make_float4(0.5f * (a.x * il * ga.x + b.x * ir * gb.x),
+                    0.5f * (a.y * il * ga.y + b.y * ir * gb.y),
+                    0.5f * (a.z * il * ga.z + b.z * ir * gb.z),
+                    0.5f * (a.w * il * ga.w + b.w * ir * gb.w)));
+  }
+}
+
 IX_API int ix_normed_pair_mean(const void* l, const void* r, int dtype, const float* gl,
                                const float* gr, float* out, int T, int W, float eps,
                                cudaStream_t stream) {
   if (T <= 0) return IX_OK;
   if (W <= 0) return IX_ERR_SIZE;
-  const int threads = W >= 2048 ? 512 : (W >= 512 ? 256 : 128);
-  IX_DISPATCH_DTYPE(dtype, TL,
-                    ix_launch(normed_pair_mean_kernel<TL>, dim3(T), dim3(threads), 0, stream,
-                              (const TL*)l, (const TL*)r, gl, gr, out, W, eps));
+  const size_t el = dtype == IX_F32 ? 4 : 2;
+  const bool vec = W % 4 == 0 && at_four(l, el) && at_four(r, el) && at_four(gl, 4) &&
+                   at_four(gr, 4) && at_four(out, 4);
+  const int threads = vec ? (W >= 4096 ? 512 : (W >= 1024 ? 256 : 128))
+                          : (W >= 2048 ? 512 : (W >= 512 ? 256 : 128));
+  IX_DISPATCH_DTYPE(dtype, TL, {
+    auto kern = vec ? normed_pair_mean_vec_kernel<TL> : normed_pair_mean_kernel<TL>;
+    ix_launch(kern, dim3(T), dim3(threads), 0, stream, (const TL*)l, (const TL*)r, gl, gr, out,
+              W, eps);
+  });
   return ix_launch_status();
 }
 
