@@ -66,6 +66,7 @@ class CacheGroup:
     """Layers that keep the same span of tokens share page ids and block tables."""
     window: int = 0          # 0: every token; W: the last W tokens
     layers: tuple = ()       # indices of the layers whose caches live in this group
+    keep_first: int = 0      # with a window: the first tokens of a request stay too
 
 
 @dataclass
@@ -208,8 +209,10 @@ class CacheManager:
             first_needed = new_len - grp.window + 1
             table = r.tables[g]
             i = r.first_live[g]
+            # (a page that holds one of the first tokens a windowed layer keeps visible
+            # stays; ``first_live`` then counts the pages that were looked at)
             while i < len(table) and (i + 1) * self.page_size <= first_needed:
-                if table[i] >= 0:
+                if table[i] >= 0 and i * self.page_size >= grp.keep_first:
                     self.pools[g].release(table[i])
                     table[i] = -1
                 i += 1
@@ -249,11 +252,22 @@ def groups_for(cache_needs_per_layer) -> List[CacheGroup]:
     """Group layers by the span of tokens their paged needs keep.
 
     ``cache_needs_per_layer[i]`` is the list of needs of layer ``i``'s mixer.  The span
-    alone decides the group: a page is a span of tokens, so layers whose records differ
-    in shape or number of entries can share page numbers and block tables."""
-    by_window: Dict[int, List[int]] = {}
+    alone decides the group (the window, and how many first tokens stay beside it): a page
+    is a span of tokens, so layers whose records differ in shape or number of entries can
+    share page numbers and block tables."""
+    by_span: Dict[tuple, List[int]] = {}
     for i, needs in enumerate(cache_needs_per_layer):
         for need in needs:
-            if is_paged_need(need) and i not in by_window.setdefault(int(need.window), []):
-                by_window[int(need.window)].append(i)
-    return [CacheGroup(window=w, layers=tuple(ls)) for w, ls in sorted(by_window.items())]
+            if is_paged_need(need):
+                key = span_key(need)
+                if i not in by_span.setdefault(key, []):
+                    by_span[key].append(i)
+    return [CacheGroup(window=w, layers=tuple(ls), keep_first=k)
+            for (w, k), ls in sorted(by_span.items())]
+
+
+def span_key(need) -> tuple:
+    """(window, first tokens kept beside it) of a paged need; without a window every token
+    stays and the second number says nothing."""
+    window = int(need.window)
+    return (window, int(getattr(need, "keep_first", 0)) if window > 0 else 0)

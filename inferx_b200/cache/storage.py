@@ -15,7 +15,7 @@ from typing import Dict, List
 import torch
 
 from ..parts.base import LayerCache, PagedKvNeed, StateNeed
-from .manager import CacheManager, is_paged_need
+from .manager import CacheManager, is_paged_need, span_key
 
 
 class CacheStorage:
@@ -25,11 +25,12 @@ class CacheStorage:
         self.paged: Dict[int, Dict[str, torch.Tensor]] = {}
         self.group_of_layer: Dict[int, int] = {}
         self.state: Dict[int, Dict[str, torch.Tensor]] = {}
-        window_to_group = {g.window: i for i, g in enumerate(manager.groups)}
+        span_to_group = {(g.window, getattr(g, "keep_first", 0)): i
+                         for i, g in enumerate(manager.groups)}
         for layer, needs in enumerate(cache_needs_per_layer):
             for need in needs:
                 if is_paged_need(need):
-                    g = window_to_group[int(need.window)]
+                    g = span_to_group[span_key(need)]
                     if self.group_of_layer.setdefault(layer, g) != g:
                         raise TypeError(f"layer {layer}: paged needs with different windows; "
                                         "one block table addresses a layer's pages")
@@ -69,6 +70,12 @@ class CacheStorage:
                 group=self.group_of_layer.get(src, -1), pages=self.paged.get(src, {}),
                 writes=e.writes_cache, state=self.state.get(src, {})))
         return out
+
+    def unit_cache(self, unit: int) -> LayerCache:
+        """The cache of one unit by its index among the needs (for a part that is not a
+        layer of the schedule: the embedding's state, say)."""
+        return LayerCache(group=self.group_of_layer.get(unit, -1), pages=self.paged.get(unit, {}),
+                          writes=True, state=self.state.get(unit, {}))
 
     def zero_slots(self, slots) -> None:
         if not slots:

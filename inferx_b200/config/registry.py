@@ -68,6 +68,10 @@ def _register_builtin():
     from .mapovik_config import MapovikConfig
     register_architecture(MapovikConfig.ARCHITECTURE, MapovikConfig.from_json,
                           mapovik.build_spec, replace=True)
+    from ..models import fudulix
+    from .fudulix_config import FudulixConfig
+    register_architecture(FudulixConfig.ARCHITECTURE, FudulixConfig.from_json,
+                          fudulix.build_spec, replace=True)
 
 
 _register_builtin()

@@ -160,6 +160,9 @@ class Executor:
         self.vocab = model.spec.vocab_size
         self.caches = storage.layer_caches(model.spec.schedule,
                                            getattr(model, "cache_unit", None))
+        # state of parts that are not layers of the schedule (the embedding's) follows
+        for unit in getattr(model, "extra_cache_units", ()):
+            self.caches.append(storage.unit_cache(unit))
         self.steps_run = 0
         self.use_graphs = bool(use_graphs) and self.device.type == "cuda"
         self._graphs = GraphCache()
@@ -313,6 +316,7 @@ class Executor:
             groups.append(GroupView(
                 block_table=seg(_FIXED_SEGS + 2 * g + 1).view(lay.S, lay.widths[g]),
                 slots=seg(_FIXED_SEGS + 2 * g), page_size=mgr.page_size, window=grp.window,
+                keep_first=getattr(grp, "keep_first", 0),
                 first_live=None if static else list(lay.first_live[g])))
         max_kv = max(lay.kv_lens)
         if static:   # a captured graph must hold for every length its table width allows

@@ -1,6 +1,6 @@
 # importing a module registers the kinds it defines
-from . import (attention, feed_forward, latent_attention, linear_recurrence,  # noqa: F401
-               norm, position, state_space, token_shift)
+from . import (attention, embedding, feed_forward, latent_attention,  # noqa: F401
+               linear_recurrence, norm, position, state_space, token_shift)
 from .base import (BuildContext, GroupView, LayerCache, PagedKvNeed, StateNeed,  # noqa: F401
                    StepContext)
 from .block import Block, DecoderModel  # noqa: F401

@@ -12,7 +12,7 @@ from __future__ import annotations
 import torch
 
 from ..weights.loader import TensorDecl
-from .base import PagedKvNeed
+from .base import PagedKvNeed, StateNeed
 from .registry import build_part, register_part
 
 
@@ -197,3 +197,123 @@ class TiedKvAttentionMixer:
 
 
 register_part("mixer", "attention_tied_kv", TiedKvAttentionMixer)
+
+
+CONV_INPUTS = "attention_conv_inputs"
+
+
+class PreparedAttentionMixer:
+    """Grouped-query attention over a window whose q, k and v pass, between the projection
+    and the cache, a short causal convolution, a norm of the whole q and k rows, the
+    rotation, a division of every q and k head by its root mean square and a blend of the
+    values with those an earlier layer left for this step - each only where the spec asks
+    for it.  The window may keep a request's first tokens visible and the softmax may have
+    one added to its denominator.  Keys and values live in the framework's pages (the
+    value pages as wide as the value heads); the convolutions' last inputs in the state
+    slots.  Norms, angles, scores and weights are fp32 in every element type."""
+
+    def __init__(self, spec, ctx, prefix: str):
+        self.spec, self.ctx, self.prefix = spec, ctx, prefix
+        s = spec
+        if s.heads % s.kv_heads:
+            raise ValueError(f"{prefix}: {s.heads} heads do not split over {s.kv_heads} "
+                             "key/value heads")
+        if s.value_mix not in ("none", "source", "mix"):
+            raise ValueError(f"{prefix}: value_mix {s.value_mix!r}")
+        self.vdim = int(s.value_dim or s.head_dim)
+        self.dq, self.dk = s.heads * s.head_dim, s.kv_heads * s.head_dim
+        self.dv = s.kv_heads * self.vdim
+        self.taps = int(s.conv_taps) if s.conv_taps and s.conv_taps > 1 else 1
+        self.has_conv = bool(s.conv_taps)
+        self.position = build_part("position", s.position, ctx, prefix)
+        if self.position is not None and not hasattr(self.position, "pair_table"):
+            raise ValueError(f"{prefix}: the position encoding must give a table of pair "
+                             "frequencies")
+        self.names = dict(s.names)
+        self.qkv_w = self.o_w = self.conv_w = self.q_gain = self.k_gain = self.lam = None
+
+    def check_limits(self):
+        check = getattr(self.ctx.ops, "check_attention_limits", None)
+        if check is not None:
+            s = self.spec
+            check(s.heads, s.kv_heads, s.head_dim, self.ctx.dtype, self.prefix, allow_odd=True)
+            check(s.heads, s.kv_heads, self.vdim, self.ctx.dtype, self.prefix, allow_odd=True)
+        check = getattr(self.ctx.ops, "check_delta_limits", None)
+        if check is not None and self.taps > 1:
+            check(1, self.taps, self.prefix)
+
+    def _n(self, key):
+        return f"{self.prefix}.{self.names[key]}"
+
+    def tensors(self):
+        s = self.spec
+        decls = [TensorDecl(self._n("q"), (self.dq, s.hidden)),
+                 TensorDecl(self._n("k"), (self.dk, s.hidden)),
+                 TensorDecl(self._n("v"), (self.dv, s.hidden)),
+                 TensorDecl(self._n("o"), (s.hidden, s.heads * self.vdim))]
+        if self.has_conv:
+            decls += [TensorDecl(self._n("q_conv"), (self.dq, s.conv_taps), keep="float32"),
+                      TensorDecl(self._n("k_conv"), (self.dk, s.conv_taps), keep="float32"),
+                      TensorDecl(self._n("v_conv"), (self.dv, s.conv_taps), keep="float32")]
+        if s.projection_norm:
+            decls += [TensorDecl(self._n("q_norm"), (self.dq,), keep="float32", init="gain"),
+                      TensorDecl(self._n("k_norm"), (self.dk,), keep="float32", init="gain")]
+        if s.value_mix != "none":
+            # the layer that leaves its values has the scalar too; it is not used there
+            decls.append(TensorDecl(self._n("mix"), (), keep="float32", init="bias"))
+        return decls
+
+    def bind(self, w):
+        s = self.spec
+        self.qkv_w = torch.cat([w[self._n("q")], w[self._n("k")], w[self._n("v")]],
+                               dim=0).contiguous()
+        self.o_w = w[self._n("o")]
+        if self.has_conv:
+            self.conv_w = torch.cat([w[self._n("q_conv")], w[self._n("k_conv")],
+                                     w[self._n("v_conv")]], dim=0).contiguous()
+        if s.projection_norm:
+            self.q_gain, self.k_gain = w[self._n("q_norm")], w[self._n("k_norm")]
+        if s.value_mix == "mix":
+            self.lam = w[self._n("mix")].reshape(1).contiguous()
+
+    def cache_needs(self):
+        s = self.spec
+        needs = [PagedKvNeed(s.kv_heads, s.head_dim, s.window,
+                             entry_dims=(s.head_dim, self.vdim),
+                             keep_first=s.keep_first if s.window > 0 else 0)]
+        if self.taps > 1:
+            needs.append(StateNeed(CONV_INPUTS, (self.taps - 1, self.dq + self.dk + self.dv),
+                                   torch.float32))
+        return needs
+
+    def forward(self, x, step, cache):
+        s, ops = self.spec, self.ctx.ops
+        group = step.groups[cache.group]
+        qkv = ops.linear(x, self.qkv_w)                     # [T, q | k | v]
+        if self.has_conv:
+            qkv = ops.causal_conv(qkv, self.conv_w, None, cache.state.get(CONV_INPUTS), step,
+                                  silu=False)
+        key = f"value_mix:{s.value_mix_key}"
+        earlier = None
+        if s.value_mix == "mix":
+            if key not in step.shared:
+                raise ValueError(f"{self.prefix}: no earlier layer left values to mix with")
+            earlier = step.shared[key]
+        freq, magnitude, rot, interleaved = (None, 1.0, 0, False)
+        if self.position is not None:
+            freq, magnitude, rot, interleaved = self.position.pair_table()
+        q = ops.attention_prepare(
+            qkv, step.positions, freq, magnitude, rot, interleaved, s.heads, s.kv_heads,
+            s.head_dim, self.vdim, self.q_gain, self.k_gain, s.norm_eps, s.head_unit_norm,
+            earlier, self.lam, cache.k if cache.writes else None,
+            cache.v if cache.writes else None, group.slots if cache.writes else None)
+        if s.value_mix == "source":
+            # this layer's values as projected (and convolved): a view of its own rows
+            step.shared[key] = qkv[:, self.dq + self.dk:]
+        attn = ops.paged_attention(q, cache.k, cache.v, group.block_table, step, s.window,
+                                   s.scale, fp32_weights=True,
+                                   keep_first=s.keep_first if s.window > 0 else 0, sink=s.sink)
+        return ops.linear(attn.view(step.num_tokens, s.heads * self.vdim), self.o_w)
+
+
+register_part("mixer", "attention_prepared", PreparedAttentionMixer)

@@ -58,6 +58,8 @@ class PagedKvNeed:
     dtype: Optional[torch.dtype] = None
     # a head size per entry where they differ (values wider than keys, say); None: head_dim
     entry_dims: Optional[Tuple[int, ...]] = None
+    # with a window: the first ``keep_first`` tokens of a request stay as well
+    keep_first: int = 0
 
     def dim_of(self, index: int) -> int:
         return self.head_dim if self.entry_dims is None else int(self.entry_dims[index])
@@ -87,6 +89,7 @@ class GroupView:
     # host mirror: per sequence, the index of the first page still held (pages before it
     # were given back as the window passed them); None in a step recorded for replay
     first_live: Optional[List[int]] = None
+    keep_first: int = 0         # tokens at the start of a request that a windowed group keeps
 
 
 @dataclass
@@ -123,6 +126,10 @@ class StepContext:
     # the two parts of a mixed batch to different kernels without gathering.
     num_decode_seqs: int = 0
     cu_q_prompt: Optional[torch.Tensor] = None   # [S - num_decode_seqs + 1] int32
+    # What one layer leaves for later layers of the same step (the values a later layer
+    # mixes with its own, for instance), by a key the two agree on.  It lives as long as
+    # the step; nothing in it is carried to the next one.
+    shared: Dict[str, Any] = field(default_factory=dict)
 
 
 @dataclass

@@ -165,6 +165,10 @@ class DecoderModel:
         self.final_norm = build_part("norm", spec.final_norm, ctx, spec.final_norm_name)
         self.embed_position = build_part("position", getattr(spec, "embed_position", None), ctx,
                                          spec.embed_name)
+        # a part that forms the stream from the tokens in a way of its own (it gets the
+        # embedding table and may keep state per request), or None: the table's rows
+        self.embedding = build_part("embedding", getattr(spec, "embedding", None), ctx,
+                                    spec.embed_name)
         self.embed = None
         self.head = None
         self.stream_tables = {}      # checkpoint name -> fp32 [rows, hidden]
@@ -180,6 +184,11 @@ class DecoderModel:
                         if getattr(e, "cache_copy", 0)})
         self.cache_units = [(i, 0) for i in range(len(self.blocks))] + extra
         self._unit_index = {u: i for i, u in enumerate(self.cache_units)}
+        # cache units of parts outside the schedule come after the layers' (their caches
+        # follow the schedule's in the list ``forward`` gets)
+        self.extra_cache_units = []
+        if self.embedding is not None and self.embedding.cache_needs():
+            self.extra_cache_units.append(len(self.cache_units))
         self._keeps_embedding = any(
             getattr(e, "before", None) is not None
             and (e.before.embedding or getattr(e.before, "project", None))
@@ -217,6 +226,8 @@ class DecoderModel:
             for part in b.parts():
                 decls += part.tensors()
         decls += self.final_norm.tensors()
+        if self.embedding is not None:
+            decls += self.embedding.tensors()
         return decls
 
     def load(self, source: wl.WeightSource, where: str = "weights") -> None:
@@ -237,12 +248,17 @@ class DecoderModel:
             for part in b.parts():
                 part.bind(fetch(part.tensors()))
         self.final_norm.bind(fetch(self.final_norm.tensors()))
+        if self.embedding is not None:
+            self.embedding.bind(fetch(self.embedding.tensors()))
 
     # -- cache needs -------------------------------------------------------
     def cache_needs(self) -> List[list]:
         """Per cache unit (a layer, or one of several copies of a layer's cache), what the
         layer's mixer wants kept between steps."""
-        return [list(self.blocks[layer].cache_needs()) for layer, _ in self.cache_units]
+        needs = [list(self.blocks[layer].cache_needs()) for layer, _ in self.cache_units]
+        if self.extra_cache_units:
+            needs.append(list(self.embedding.cache_needs()))
+        return needs
 
     def cache_unit(self, entry) -> int:
         """The cache unit a schedule entry reads and writes."""
@@ -293,7 +309,10 @@ class DecoderModel:
         ops = self.ctx.ops
         if hasattr(ops, "set_dependent_launch"):
             ops.set_dependent_launch(step.num_tokens <= ops.DEPENDENT_LAUNCH_MAX_TOKENS)
-        if self.embed_position is not None:
+        if self.embedding is not None:
+            own = caches[len(self.spec.schedule)] if self.extra_cache_units else None
+            resid = self.embedding.forward(self.embed, step, own)
+        elif self.embed_position is not None:
             resid = self.embed_position.embed(self.embed, step.token_ids, step.positions,
                                               self.spec.embed_scale)
         elif self.spec.embed_scale != 1.0:

@@ -80,14 +80,79 @@ class ClampedGluFeedForward:
         return ops.linear(act, self.down_w, out_dtype=torch.float32)
 
 
+class BiasedGluFeedForward:
+    """``down(act(gate h + b_g) * (up h + b_u)) + b_d``: a gated unit with a bias on each of
+    its three projections and the tanh form of gelu (or silu) on the gate.  Gate and up
+    are one product over concatenated weights; their biases and the activation are one
+    pass over its result; the last bias travels with the output as the vector of a pending
+    sum, so the norm that adds the output to the stream adds it in the same pass."""
+
+    def __init__(self, spec, ctx, prefix: str):
+        self.spec, self.ctx, self.prefix = spec, ctx, prefix
+        if spec.activation not in ("gelu_tanh", "silu"):
+            raise ValueError(f"{prefix}: activation {spec.activation!r}")
+        self.gate_up_w = self.down_w = self.gate_up_b = self.down_b = None
+
+    def _bias_names(self):
+        return [f"{self.prefix}.{n}{self.spec.bias_suffix}" for n in self.spec.names]
+
+    def tensors(self):
+        s, p = self.spec, self.prefix
+        g, u, d = s.names
+        decls = [TensorDecl(f"{p}.{g}", (s.intermediate, s.hidden)),
+                 TensorDecl(f"{p}.{u}", (s.intermediate, s.hidden)),
+                 TensorDecl(f"{p}.{d}", (s.hidden, s.intermediate))]
+        if s.bias:
+            gb, ub, db = self._bias_names()
+            decls += [TensorDecl(gb, (s.intermediate,), keep="float32", init="bias"),
+                      TensorDecl(ub, (s.intermediate,), keep="float32", init="bias"),
+                      TensorDecl(db, (s.hidden,), keep="float32", init="bias")]
+        return decls
+
+    def bind(self, w):
+        p = self.prefix
+        g, u, d = self.spec.names
+        self.gate_up_w = torch.cat([w[f"{p}.{g}"], w[f"{p}.{u}"]], dim=0).contiguous()
+        self.down_w = w[f"{p}.{d}"]
+        if self.spec.bias:
+            gb, ub, db = self._bias_names()
+            self.gate_up_b = torch.cat([w[gb], w[ub]], dim=0).contiguous()
+            self.down_b = w[db]
+
+    def forward(self, x, step=None):
+        from .base import PendingSum
+        ops = self.ctx.ops
+        act = ops.glu_bias_act(ops.linear(x, self.gate_up_w), self.gate_up_b,
+                               self.spec.activation)
+        y = ops.linear(act, self.down_w)
+        if self.down_b is None:
+            return y
+        return PendingSum(terms=[y], vector=self.down_b, dtype=self.ctx.dtype)
+
+
 _SIDE_STREAMS: dict = {}
 
 
 class MoeFeedForward:
     def __init__(self, spec, ctx, prefix: str):
         self.spec, self.ctx, self.prefix = spec, ctx, prefix
-        if spec.top_k > spec.num_experts:
+        self.identity = int(getattr(spec, "identity_experts", 0) or 0)
+        self.outputs = spec.num_experts + self.identity      # what the router scores
+        self.group_count = int(getattr(spec, "group_count", 0) or 0)
+        self.group_keep = int(getattr(spec, "group_keep", 0) or 0)
+        self.renorm_eps = float(getattr(spec, "renorm_eps", -1.0))
+        self.correction_name = getattr(spec, "correction_name", None)
+        self.correction = None
+        self.ruled = bool(self.identity or self.group_count or self.correction_name
+                          or self.renorm_eps >= 0)
+        if spec.top_k > self.outputs:
             raise ValueError("top_k exceeds the number of experts")
+        if self.group_count and (self.outputs % self.group_count
+                                 or not 0 < self.group_keep <= self.group_count
+                                 or self.group_keep * (self.outputs // self.group_count)
+                                 < spec.top_k):
+            raise ValueError(f"{prefix}: {self.group_keep} of {self.group_count} groups over "
+                             f"{self.outputs} router outputs, {spec.top_k} chosen")
         self.router_w = self.expert_gate_up = self.expert_down = None
         self.shared = None
         self._shared_bytes = 0
@@ -101,7 +166,10 @@ class MoeFeedForward:
     def check_limits(self):
         check = getattr(self.ctx.ops, "check_router_limits", None)
         if check is not None:
-            check(self.spec.hidden, self.spec.num_experts, self.spec.top_k, self.prefix)
+            check(self.spec.hidden, self.outputs, self.spec.top_k, self.prefix)
+        check = getattr(self.ctx.ops, "check_router_group_limits", None)
+        if check is not None and self.group_count:
+            check(self.group_count, self.prefix)
         if self.shared is not None and hasattr(self.shared, "check_limits"):
             self.shared.check_limits()
 
@@ -116,7 +184,10 @@ class MoeFeedForward:
 
     def tensors(self):
         s, p = self.spec, self.prefix
-        decls = [TensorDecl(self._router_name(), (s.num_experts, s.hidden), keep="float32")]
+        decls = [TensorDecl(self._router_name(), (self.outputs, s.hidden), keep="float32")]
+        if self.correction_name:
+            decls.append(TensorDecl(f"{p}.{self.correction_name}", (self.outputs,),
+                                    keep="float32", init="bias"))
         for e in range(s.num_experts):
             g, u, d = self._expert_names(e)
             decls += [
@@ -134,6 +205,8 @@ class MoeFeedForward:
     def bind(self, w):
         s, p = self.spec, self.prefix
         self.router_w = w[self._router_name()]
+        if self.correction_name:
+            self.correction = w[f"{p}.{self.correction_name}"]
         gu = torch.empty((s.num_experts, 2 * s.expert_intermediate, s.hidden),
                          dtype=self.ctx.dtype, device=self.ctx.device)
         dn = torch.empty((s.num_experts, s.hidden, s.expert_intermediate),
@@ -222,9 +295,20 @@ class MoeFeedForward:
             side = self._side_stream()
             main = torch.cuda.current_stream(x.device)
             ready = main.record_event()        # x is there; what follows is not waited for
-        topk_w, topk_idx, shared_logit = ops.router_topk(
-            x, self.router_w, s.top_k, s.renormalize, s.routed_scale, extra_w=self.shared_gate_w)
-        offsets, rows, dest = ops.moe_dispatch(topk_idx, s.num_experts)
+        if self.ruled:
+            topk_w, topk_idx, shared_logit = ops.router_topk(
+                x, self.router_w, s.top_k, s.renormalize, s.routed_scale,
+                extra_w=self.shared_gate_w, correction=self.correction,
+                group_count=self.group_count, group_keep=self.group_keep,
+                renorm_eps=self.renorm_eps)
+        else:
+            topk_w, topk_idx, shared_logit = ops.router_topk(
+                x, self.router_w, s.top_k, s.renormalize, s.routed_scale,
+                extra_w=self.shared_gate_w)
+        # identity experts are the router's last outputs: the stable dispatch puts their
+        # rows behind every expert's, where no product writes
+        all_offsets, rows, dest = ops.moe_dispatch(topk_idx, self.outputs)
+        offsets = all_offsets[:s.num_experts + 1] if self.identity else all_offsets
         if ready is not None:
             side.wait_event(ready)
             with torch.cuda.stream(side):
@@ -233,6 +317,9 @@ class MoeFeedForward:
         # `offsets` was written by the dispatch, two launches back: the down product may
         # start on its weights while the gate/up product drains
         y = ops.grouped_down(act, offsets, self.expert_down, offsets_settled=True)
+        if self.identity:
+            # a token's row for an identity expert is its own input
+            ops.identity_rows(x, rows, all_offsets, s.num_experts, y)
         if side is not None:
             main.wait_stream(side)
         elif self.shared is not None:
@@ -329,4 +416,5 @@ register_part("feed_forward", "swiglu", SwiGluFeedForward)
 register_part("feed_forward", "moe", MoeFeedForward)
 register_part("feed_forward", "clamped_glu", ClampedGluFeedForward)
 register_part("feed_forward", "relu_squared", ReluSquaredFeedForward)
+register_part("feed_forward", "glu_biased", BiasedGluFeedForward)
 register_part("feed_forward", "moe_table", TableMoeFeedForward)

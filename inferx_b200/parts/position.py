@@ -111,3 +111,63 @@ class SinusoidAdded:
 
 
 register_part("position", "sinusoid_added", SinusoidAdded)
+
+
+class ScaledRotary:
+    """Rotation of pairs of a head's first ``rotary_dim`` entries, in either pairing, with
+    the frequencies stretched by wavelength or by a ramp over the pair index (the spec
+    says how).  ``pair_table()`` gives (frequency per pair as fp32 [rotary_dim / 2], the
+    factor on cos and sin, rotary_dim, whether pairs are neighbours).  The frequencies are
+    formed in float64 and rounded once; the kernel multiplies position and frequency, and
+    takes cos and sin, in fp32."""
+
+    def __init__(self, spec, ctx, prefix: str):
+        import math
+        self.spec = spec
+        r = spec.rotary_dim
+        if r % 2 or r > spec.head_dim or r < 0:
+            raise ValueError(f"rotary_dim {r} must be even and at most {spec.head_dim}")
+        if spec.layout not in ("half", "interleaved"):
+            raise ValueError(f"rotary layout {spec.layout!r} is not 'half' or 'interleaved'")
+        f = [float(spec.theta) ** (-2.0 * i / max(r, 1)) for i in range(r // 2)]
+        self.magnitude = 1.0
+        sc = spec.scaling
+        if sc is not None and sc[0] == "wavelength":
+            _, factor, low, high, original = sc
+            out = []
+            for v in f:
+                wavelength = 2.0 * math.pi / v
+                if wavelength < original / high:
+                    out.append(v)
+                elif wavelength > original / low:
+                    out.append(v / factor)
+                else:
+                    t = (original / wavelength - low) / (high - low)
+                    out.append((1.0 - t) * v / factor + t * v)
+            f = out
+        elif sc is not None and sc[0] == "ramp":
+            _, factor, original, fast, slow = sc
+
+            def pair_with_turns(turns):
+                return r * math.log(original / (2.0 * math.pi * turns)) / (
+                    2.0 * math.log(spec.theta))
+            lo = max(math.floor(pair_with_turns(fast)), 0)
+            hi = min(math.ceil(pair_with_turns(slow)), r - 1)
+            ramp = [min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0) for i in range(r // 2)]
+            f = [v / factor * t + v * (1.0 - t) for v, t in zip(f, ramp)]
+            self.magnitude = 0.1 * math.log(factor) + 1.0
+        elif sc is not None:
+            raise ValueError(f"rotary scaling {sc[0]!r} is not 'wavelength' or 'ramp'")
+        self.freq = torch.tensor(f, dtype=torch.float64).to(torch.float32).to(ctx.device)
+
+    def tensors(self):
+        return []
+
+    def bind(self, weights):
+        pass
+
+    def pair_table(self):
+        return self.freq, self.magnitude, self.spec.rotary_dim, self.spec.layout == "interleaved"
+
+
+register_part("position", "rope_scaled", ScaledRotary)

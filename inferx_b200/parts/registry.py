@@ -1,8 +1,8 @@
 """Registry from (role, kind) to the class that runs a spec of that kind.
 
 Roles: ``"norm"``, ``"position"``, ``"mixer"``, ``"feed_forward"``, ``"mixer_input"``
-(a transform of what the mixer reads) and ``"block"`` (the arrangement of one layer's
-parts).  A new kind
+(a transform of what the mixer reads), ``"embedding"`` (what forms the stream from the
+tokens) and ``"block"`` (the arrangement of one layer's parts).  A new kind
 of part is added by registering its class here; nothing else in the package
 names the kinds.
 """
@@ -10,7 +10,7 @@ from __future__ import annotations
 
 from typing import Any, Dict
 
-ROLES = ("norm", "position", "mixer", "feed_forward", "block", "mixer_input")
+ROLES = ("norm", "position", "mixer", "feed_forward", "block", "mixer_input", "embedding")
 _PARTS: Dict[str, Dict[str, type]] = {r: {} for r in ROLES}
 
 

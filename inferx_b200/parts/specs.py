@@ -301,6 +301,94 @@ class TableMoeSpec:
 
 
 @dataclass(frozen=True)
+class ScaledRopeSpec:
+    """Rotary encoding of the first ``rotary_dim`` entries of each head with a choice of
+    pairing and of frequency stretching.  ``layout`` "half" pairs entry i with entry
+    i + rotary_dim / 2, "interleaved" pairs 2i with 2i + 1; pair i turns by position *
+    f_i with f_i = theta^(-2i / rotary_dim).  ``scaling`` is None or a tuple:
+    ("wavelength", factor, low, high, original): with l = 2 pi / f, f stays where
+    l < original / high, becomes f / factor where l > original / low, and in between
+    (1 - s) f / factor + s f with s = (original / l - low) / (high - low);
+    ("ramp", factor, original, fast, slow): with pair(t) = rotary_dim ln(original /
+    (2 pi t)) / (2 ln theta), lo = max(floor(pair(fast)), 0), hi = min(ceil(pair(slow)),
+    rotary_dim - 1) and r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1) the frequency is
+    f_i / factor * r_i + f_i (1 - r_i), and cos and sin are multiplied by
+    0.1 ln(factor) + 1."""
+    head_dim: int
+    rotary_dim: int
+    theta: float
+    layout: str = "half"
+    scaling: Any = None
+    kind: str = "rope_scaled"
+
+
+@dataclass(frozen=True)
+class PreparedAttentionSpec:
+    """Grouped-query softmax attention whose queries, keys and values are prepared between
+    the projection and the cache: in this order, a causal convolution over time of
+    ``conv_taps`` taps per channel of q, k and v (no bias, no activation; 0 or 1: none;
+    the last taps - 1 projected rows are state per request), an RMS norm of the whole q
+    row and of the whole k row with gains (``projection_norm``), the rotation
+    (``position``), a division of every q and k head by its own root mean square
+    (``head_unit_norm``), and the value mixing: with ``value_mix`` "mix" the values become
+    (1 - lambda) v + lambda v0, v0 being the values of the same token left by the layer
+    whose ``value_mix`` is "source" (the first of the model that mixes) and lambda a
+    scalar of the checkpoint; what is mixed is what the cache holds.  A query at position
+    i sees key j <= i when i - j < ``window`` (0: all) or j < ``keep_first``.  With
+    ``sink`` one is added to the softmax's denominator (a key of score 0 without a
+    value).  Scores are (q . k) * scale; scores, weights and their products with the values
+    are 32-bit arithmetic in every element type."""
+    hidden: int
+    heads: int
+    kv_heads: int
+    head_dim: int
+    value_dim: int
+    scale: float
+    window: int
+    position: Any
+    norm_eps: float
+    keep_first: int = 0
+    sink: bool = False
+    conv_taps: int = 0
+    projection_norm: bool = False
+    head_unit_norm: bool = False
+    value_mix: str = "none"          # "none" | "source" | "mix"
+    value_mix_key: str = "values"    # layers that mix with one another share the key
+    names: tuple = (("q", "q"), ("k", "k"), ("v", "v"), ("o", "o"), ("q_norm", "q.norm"),
+                    ("k_norm", "k.norm"), ("q_conv", "q.conv"), ("k_conv", "k.conv"),
+                    ("v_conv", "v.conv"), ("mix", "vmix"))
+    kind: str = "attention_prepared"
+
+
+@dataclass(frozen=True)
+class BiasedGluSpec:
+    """down(act(gate h + b_g) * (up h + b_u)) + b_d with ``activation`` "gelu_tanh"
+    (0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))) or "silu"; ``bias`` off: no b."""
+    hidden: int
+    intermediate: int
+    activation: str = "gelu_tanh"
+    bias: bool = True
+    names: tuple = ("gate", "up", "down")
+    bias_suffix: str = ".b"
+    kind: str = "glu_biased"
+
+
+@dataclass(frozen=True)
+class PairEmbeddingSpec:
+    """The stream starts as norm(embed[token] + pair[row]) with row = (previous token *
+    mul_prev + token * mul_cur) mod buckets, row ``buckets`` (the table's last) for a
+    sequence's first token, and ``norm`` an RMS norm spec whose gain is ``norm_name``.
+    The previous token is state per request."""
+    buckets: int
+    mul_prev: int
+    mul_cur: int
+    norm: Any
+    table_name: str = "bigram"
+    norm_name: str = "embed.norm"
+    kind: str = "pair_embedding"
+
+
+@dataclass(frozen=True)
 class SwiGluSpec:
     hidden: int
     intermediate: int
@@ -326,6 +414,19 @@ class MoeSpec:
     router_name: str = "gate.weight"
     expert_names: tuple = ("experts.{e}.gate_proj.weight", "experts.{e}.up_proj.weight",
                            "experts.{e}.down_proj.weight")
+    # The router may have more outputs than there are experts: its last
+    # ``identity_experts`` outputs stand for experts that return their input.  With
+    # ``correction_name`` a vector of the checkpoint is added to the scores for the choice
+    # alone (the weights stay the plain scores).  With ``group_count`` > 0 the router's
+    # outputs form that many equal groups of neighbours, a group's value is its largest
+    # score (with the correction), and only outputs of the ``group_keep`` best groups can
+    # be chosen.  ``renorm_eps`` >= 0: the chosen weights are divided by (their sum +
+    # renorm_eps) instead of the guarded division ``renormalize`` does.
+    identity_experts: int = 0
+    correction_name: Optional[str] = None
+    group_count: int = 0
+    group_keep: int = 0
+    renorm_eps: float = -1.0
     kind: str = "moe"
 
 
@@ -406,3 +507,4 @@ class ModelSpec:
     embed_scale: float = 1.0     # the residual stream starts as embed[token] * embed_scale
     logit_scale: float = 1.0     # the head's products are multiplied by this
     embed_position: Any = None   # a position spec whose vector is added to the embedding
+    embedding: Any = None        # a spec of what forms the stream from the tokens (None: the table's rows)

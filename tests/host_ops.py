@@ -94,7 +94,7 @@ def append_kv(k, v, k_cache, v_cache, slots):
 
 
 def paged_attention_generic(q, k_cache, v_cache, block_table, seq_of_token, positions, window,
-                            scale, softcap=0.0):
+                            scale, softcap=0.0, keep_first=0, sink=False):
     T, heads, hd = q.shape
     P, kvh, page, _ = k_cache.shape
     rep = heads // kvh
@@ -103,6 +103,8 @@ def paged_attention_generic(q, k_cache, v_cache, block_table, seq_of_token, posi
         s, pos = int(seq_of_token[t]), int(positions[t])
         start = max(0, pos - window + 1) if window > 0 else 0
         kp = torch.arange(start, pos + 1)
+        if keep_first > 0 and start > 0:      # the request's first tokens stay visible
+            kp = torch.cat([torch.arange(0, min(keep_first, start)), kp])
         pages = block_table[s][(kp // page).long()].long()
         assert (pages >= 0).all(), "attention reads a page that was given back"
         offs = (kp % page).long()
@@ -113,21 +115,55 @@ def paged_attention_generic(q, k_cache, v_cache, block_table, seq_of_token, posi
             sc = (keys @ _f(q[t, h])) * scale
             if softcap > 0:
                 sc = softcap * torch.tanh(sc / softcap)
-            p = torch.exp(sc - sc.max())
-            out[t, h] = (p[:, None] * vals).sum(0) / p.sum()
+            top = torch.clamp(sc.max(), min=0.0) if sink else sc.max()
+            p = torch.exp(sc - top)
+            # the sink: a key of score 0 that has no value
+            den = p.sum() + (torch.exp(-top) if sink else 0.0)
+            out[t, h] = (p[:, None] * vals).sum(0) / den
     return out.to(q.dtype)
 
 
 def paged_attention(q, k_cache, v_cache, block_table, step, window, scale, softcap=0.0,
-                    fp32_weights=False):
+                    fp32_weights=False, keep_first=0, sink=False):
     return paged_attention_generic(q, k_cache, v_cache, block_table, step.seq_of_token,
-                                   step.positions, window, scale, softcap)
+                                   step.positions, window, scale, softcap, keep_first, sink)
 
 
-def router_topk(x, w, top_k, renormalize, scale, extra_w=None):
+def router_topk(x, w, top_k, renormalize, scale, extra_w=None, correction=None, group_count=0,
+                group_keep=0, renorm_eps=-1.0):
     logits = _f(x) @ w.T
     p = torch.softmax(logits, dim=-1)
     T, E = p.shape
+    if correction is not None or group_count or renorm_eps >= 0:
+        # the choice is by score + correction, inside the best groups; weights are the scores
+        pick = p + (correction if correction is not None else 0.0)
+        if group_count:
+            size = E // group_count
+            best = pick.view(T, group_count, size).max(-1).values
+            kept = torch.zeros(T, group_count, dtype=torch.bool)
+            work = best.clone()
+            for _ in range(group_keep):
+                top = work.max(-1).values
+                g = (work == top[:, None]).to(torch.int32).argmax(-1)
+                kept[torch.arange(T), g] = True
+                work[torch.arange(T), g] = float("-inf")
+            pick = torch.where(kept.repeat_interleave(size, dim=1), pick,
+                               torch.full_like(pick, float("-inf")))
+        tw = torch.zeros(T, top_k)
+        ti = torch.zeros(T, top_k, dtype=torch.int32)
+        for s in range(top_k):
+            top = pick.max(-1).values
+            idx = (pick == top[:, None]).to(torch.int32).argmax(-1)
+            tw[:, s] = p[torch.arange(T), idx]
+            ti[:, s] = idx.to(torch.int32)
+            pick[torch.arange(T), idx] = float("-inf")
+        tot = tw.sum(-1, keepdim=True)
+        if renorm_eps >= 0:
+            tw = tw / (tot + renorm_eps)
+        elif renormalize:
+            tw = torch.where(tot > 0, tw / tot, tw)
+        ex = (_f(x) @ extra_w) if extra_w is not None else None
+        return tw * scale, ti, ex
     tw = torch.zeros(T, top_k)
     ti = torch.zeros(T, top_k, dtype=torch.int32)
     work = p.clone()
@@ -625,3 +661,91 @@ def table_route(token_ids, table, num_experts):
 def scale_rows(x, scale):
     x *= scale
     return x
+
+
+# -- embedding from token pairs, prepared attention, biased gated unit, identity experts ----
+def embed_pair_norm(table, pair_table, gain, step, prev_state, buckets, mul_prev, mul_cur, eps):
+    ids = [int(v) for v in step.token_ids]
+    cu = [int(v) for v in step.cu_q]
+    rows = []
+    for s in range(len(cu) - 1):
+        slot = int(step.state_slot[s])
+        pos0 = int(step.q_pos0[s])
+        for t in range(cu[s], cu[s + 1]):
+            if pos0 + (t - cu[s]) == 0:
+                rows.append(buckets)
+            else:
+                prev = ids[t - 1] if t > cu[s] else int(prev_state[slot, 0])
+                rows.append((prev * mul_prev + ids[t] * mul_cur) % buckets)
+        prev_state[slot, 0] = ids[cu[s + 1] - 1]
+    x = _f(table)[torch.tensor(ids)] + _f(pair_table)[torch.tensor(rows)]
+    ms = (x * x).sum(-1, keepdim=True) / x.shape[-1]
+    return x * (1.0 / torch.sqrt(ms + eps)) * gain
+
+
+def _turn(v, positions, freq, magnitude, rot, interleaved):
+    # v [T, heads, dim] fp32
+    if not rot:
+        return v
+    a = positions.to(torch.float32)[:, None] * freq[None, :]
+    c, s = (torch.cos(a) * magnitude)[:, None, :], (torch.sin(a) * magnitude)[:, None, :]
+    out = v.clone()
+    if interleaved:
+        x, y = v[..., 0:rot:2], v[..., 1:rot:2]
+        out[..., 0:rot:2] = x * c - y * s
+        out[..., 1:rot:2] = y * c + x * s
+    else:
+        h = rot // 2
+        x, y = v[..., :h], v[..., h:rot]
+        out[..., :h] = x * c - y * s
+        out[..., h:rot] = y * c + x * s
+    return out
+
+
+def attention_prepare(qkv, positions, freq, magnitude, rot, interleaved, heads, kv_heads,
+                      head_dim, value_dim, q_gain, k_gain, eps, head_unit, earlier, lam,
+                      k_cache, v_cache, slots, want_dense_kv=False):
+    T = qkv.shape[0]
+    dq, dk = heads * head_dim, kv_heads * head_dim
+    x = _f(qkv)
+    q, k, v = x[:, :dq], x[:, dq:dq + dk], x[:, dq + dk:]
+
+    def whole(z, g):
+        ms = (z * z).sum(-1, keepdim=True) / z.shape[-1]
+        return z * (1.0 / torch.sqrt(ms + eps)) * g
+    if q_gain is not None:
+        q, k = whole(q, q_gain), whole(k, k_gain)
+    q = _turn(q.reshape(T, heads, head_dim), positions, freq, magnitude, rot, interleaved)
+    k = _turn(k.reshape(T, kv_heads, head_dim), positions, freq, magnitude, rot, interleaved)
+    if head_unit:
+        q = q * (1.0 / torch.sqrt((q * q).sum(-1, keepdim=True) / head_dim + eps))
+        k = k * (1.0 / torch.sqrt((k * k).sum(-1, keepdim=True) / head_dim + eps))
+    if earlier is not None:
+        m = float(lam.reshape(-1)[0])
+        v = (1.0 - m) * v + m * _f(earlier)
+    v = v.reshape(T, kv_heads, value_dim)
+    q, k, v = q.to(qkv.dtype), k.to(qkv.dtype), v.to(qkv.dtype)
+    if k_cache is not None:
+        _scatter(k_cache, k, slots)
+        _scatter(v_cache, v, slots)
+    return (q, k, v) if want_dense_kv else q
+
+
+def glu_bias_act(gu, bias, activation="gelu_tanh"):
+    i = gu.shape[1] // 2
+    x = _f(gu)
+    if bias is not None:
+        x = x + bias
+    g, u = x[:, :i], x[:, i:]
+    if activation == "silu":
+        a = g / (1.0 + torch.exp(-g))
+    else:
+        a = 0.5 * g * (1.0 + torch.tanh(0.7978845608028654 * (g + 0.044715 * g * g * g)))
+    return (a * u).to(gu.dtype)
+
+
+def identity_rows(x, rows, offsets, first_identity, y):
+    lo, hi = int(offsets[first_identity]), int(offsets[-1])
+    if hi > lo:
+        y[lo:hi] = x[rows[lo:hi].long()].to(y.dtype)
+    return y
