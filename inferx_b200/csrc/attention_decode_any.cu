@@ -13,6 +13,11 @@
 // kernel merges the partials.  A query's arithmetic depends on its own keys and on the
 // number of splits alone.
 //
+// `keep_first` > 0 keeps the sequence's first keep_first keys visible beside the window: the
+// walk goes over them and then over the window, as one range that is split.  `sink` adds
+// one to the softmax's denominator (a key of score 0 without a value), where the result
+// is normalised: in this kernel when the sequence is not split, else in the merge.
+//
 // Scratch: partial outputs [S, heads, splits, vd] and (max, sum) [S, heads, splits, 2], fp32.
 #include "common.cuh"
 
@@ -28,7 +33,7 @@ attn_decode_any_kernel(const TA* __restrict__ q, const TA* __restrict__ kc,
                        const int* __restrict__ kv_len, float* __restrict__ part_o,
                        float* __restrict__ part_ml, TA* __restrict__ out, int heads, int kvh,
                        int hd, int vd, int page_size, int maxb, int window, float scale,
-                       float softcap, int splits) {
+                       float softcap, int splits, int keep_first, int sink) {
   extern __shared__ float sm[];
   float* sm_acc = sm;                               // [G][DA_WARPS][vd]
   float* sm_m = sm_acc + (size_t)G * DA_WARPS * vd; // [G][DA_WARPS]
@@ -45,10 +50,14 @@ attn_decode_any_kernel(const TA* __restrict__ q, const TA* __restrict__ kc,
 
   const int len = kv_len[s];
   const int start = window > 0 ? max(0, len - window) : 0;
-  const int n = len - start;
+  // the kept first keys stand, in the walk, directly before the window: walk index j means
+  // key j - (start - kept) below `start` and key j from there on
+  const int kept = min(keep_first, start);
+  const int shift = start - kept;
+  const int n = len - shift;
   int chunk = (n + splits - 1) / splits;
   chunk = (chunk + DA_WARPS * DA_U - 1) / (DA_WARPS * DA_U) * (DA_WARPS * DA_U);
-  const int k0 = start + split * chunk;
+  const int k0 = shift + split * chunk;
   const int k1 = min(len, k0 + chunk);
   const int* bt = block_table + (size_t)s * maxb;
 
@@ -77,8 +86,9 @@ attn_decode_any_kernel(const TA* __restrict__ q, const TA* __restrict__ kc,
     bool valid[DA_U];
 #pragma unroll
     for (int u = 0; u < DA_U; ++u) {
-      const int kidx = kb + u;
-      valid[u] = kidx < k1;
+      const int kwalk = kb + u;
+      const int kidx = kwalk < start ? kwalk - shift : kwalk;
+      valid[u] = kwalk < k1;
       const int page = valid[u] ? bt[kidx / page_size] : 0;
       const size_t row = ((size_t)page * kvh + kh) * page_size + (valid[u] ? kidx % page_size : 0);
       krow[u] = kc + row * hd;
@@ -173,6 +183,12 @@ attn_decode_any_kernel(const TA* __restrict__ q, const TA* __restrict__ kc,
     }
     const size_t hrow = (size_t)s * heads + h0 + g;
     if (splits == 1) {
+      if (sink && M != -INFINITY) {
+        const float top = fmaxf(M, 0.f);
+        const float c = expf(M - top);
+        o *= c;
+        L = L * c + expf(-top);
+      }
       out[hrow * vd + d] = from_f32<TA>(L > 0.f ? o / L : 0.f);
     } else {
       part_o[(hrow * splits + split) * vd + d] = o;
@@ -187,7 +203,8 @@ attn_decode_any_kernel(const TA* __restrict__ q, const TA* __restrict__ kc,
 template <typename TA>
 __global__ void attn_decode_any_merge_kernel(const float* __restrict__ part_o,
                                              const float* __restrict__ part_ml,
-                                             TA* __restrict__ out, int vd, int splits) {
+                                             TA* __restrict__ out, int vd, int splits,
+                                             int sink) {
   IX_PDL_WAIT();
   const size_t hrow = blockIdx.x;   // s * heads + h
   const float* ml = part_ml + hrow * splits * 2;
@@ -196,12 +213,18 @@ __global__ void attn_decode_any_merge_kernel(const float* __restrict__ part_o,
   float L = 0.f;
   for (int j = 0; j < splits; ++j)
     if (ml[2 * j] != -INFINITY) L = fmaf(ml[2 * j + 1], expf(ml[2 * j] - M), L);
+  float c = 1.f;
+  if (sink && M != -INFINITY) {
+    const float top = fmaxf(M, 0.f);
+    c = expf(M - top);
+    L = L * c + expf(-top);
+  }
   for (int d = threadIdx.x; d < vd; d += blockDim.x) {
     float o = 0.f;
     for (int j = 0; j < splits; ++j)
       if (ml[2 * j] != -INFINITY)
         o = fmaf(part_o[(hrow * splits + j) * vd + d], expf(ml[2 * j] - M), o);
-    out[hrow * vd + d] = from_f32<TA>(L > 0.f ? o / L : 0.f);
+    out[hrow * vd + d] = from_f32<TA>(L > 0.f ? o * c / L : 0.f);
   }
 }
 
@@ -237,11 +260,13 @@ IX_API int ix_paged_attention_decode_any(const void* q, const void* k_cache, con
                                          float* part_ml, void* out, int act_dtype, int S, int heads,
                                          int kvh, int hd, int vd, int page_size, int max_blocks,
                                          int window, float scale, float softcap, int splits,
-                                         cudaStream_t stream) {
+                                         int keep_first, int sink, cudaStream_t stream) {
   if (S <= 0) return IX_OK;
   if (heads <= 0 || kvh <= 0 || heads % kvh != 0 || page_size <= 0 || max_blocks <= 0)
     return IX_ERR_SIZE;
-  if (hd <= 0 || hd > 512 || vd <= 0 || vd > 512 || window < 0 || splits < 1) return IX_ERR_SIZE;
+  if (hd <= 0 || hd > 512 || vd <= 0 || vd > 512 || window < 0 || splits < 1 ||
+      keep_first < 0)
+    return IX_ERR_SIZE;
   if (splits > 1 && (!part_o || !part_ml)) return IX_ERR_SIZE;
   const int rep = heads / kvh;
   const int dpl = da_dpl(hd, vd);
@@ -257,7 +282,7 @@ IX_API int ix_paged_attention_decode_any(const void* q, const void* k_cache, con
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
     ix_launch(kern, grid, dim3(DA_THREADS), smem, stream, (const TA*)q, (const TA*)k_cache,    \
               (const TA*)v_cache, block_table, kv_len, part_o, part_ml, (TA*)out, heads, kvh,  \
-              hd, vd, page_size, max_blocks, window, scale, softcap, splits);                  \
+              hd, vd, page_size, max_blocks, window, scale, softcap, splits, keep_first, sink); \
   })
 #define DA_D(DD)                                                                               \
   do {                                                                                         \
@@ -276,7 +301,7 @@ IX_API int ix_paged_attention_decode_any(const void* q, const void* k_cache, con
   if (rc != 0 || splits == 1) return rc;
   IX_DISPATCH_DTYPE(act_dtype, TA, {
     ix_launch(attn_decode_any_merge_kernel<TA>, dim3(S * heads), dim3(vd >= 128 ? 128 : 64), 0,
-              stream, (const float*)part_o, (const float*)part_ml, (TA*)out, vd, splits);
+              stream, (const float*)part_o, (const float*)part_ml, (TA*)out, vd, splits, sink);
   });
   return ix_launch_status();
 }

@@ -14,6 +14,11 @@
 // consumed in tiles of 128 keys with an online softmax.  One block owns one
 // (token, head); its arithmetic depends only on that token's own keys, never on
 // what else is in the batch or on which pages hold the keys.
+//
+// Two options of windowed attention: `keep_first` > 0 keeps the sequence's first
+// keep_first keys visible beside the window (they are walked first, as if they stood
+// directly before the window), and `sink` adds one to the softmax's denominator (a key
+// of score 0 that has no value).
 #include "common.cuh"
 
 #define ATT_TILE 128
@@ -27,7 +32,8 @@ paged_attention_generic_kernel(const TA* __restrict__ q, const TA* __restrict__ 
                                const int* __restrict__ seq_of_token,
                                const int* __restrict__ positions, TA* __restrict__ out, int heads,
                                int kvh, int hd, int vd, int page_size, int max_blocks,
-                               int window, float scale, float softcap) {
+                               int window, float scale, float softcap, int keep_first,
+                               int sink) {
   extern __shared__ float smem[];
   float* qs = smem;        // [hd]
   float* sc = smem + hd;   // [ATT_TILE]
@@ -50,11 +56,14 @@ paged_attention_generic_kernel(const TA* __restrict__ q, const TA* __restrict__ 
   float m = -INFINITY, l = 0.f;
 
   const int start = window > 0 ? max(0, pos - window + 1) : 0;
-  for (int tile0 = start; tile0 <= pos; tile0 += ATT_TILE) {
+  // the kept first keys count as positions start - kept .. start - 1 of the walk
+  const int kept = min(keep_first, start);
+  for (int tile0 = start - kept; tile0 <= pos; tile0 += ATT_TILE) {
     const int n = min(ATT_TILE, pos + 1 - tile0);
     // scores: one warp per key, lanes over the head dimension
     for (int j = warp; j < n; j += nwarps) {
-      const int kp = tile0 + j;
+      const int kw = tile0 + j;
+      const int kp = kw < start ? kw - (start - kept) : kw;
       const int page = bt[kp / page_size];
       const int off = kp % page_size;
       const TA* krow = kc + (((size_t)page * kvh + kh) * page_size + off) * hd;
@@ -81,7 +90,8 @@ paged_attention_generic_kernel(const TA* __restrict__ q, const TA* __restrict__ 
 #pragma unroll
     for (int i = 0; i < ATT_MAX_DPT; ++i) acc[i] *= corr;
     for (int j = 0; j < n; ++j) {
-      const int kp = tile0 + j;
+      const int kw = tile0 + j;
+      const int kp = kw < start ? kw - (start - kept) : kw;
       const int page = bt[kp / page_size];
       const int off = kp % page_size;
       const TA* vrow = vc + (((size_t)page * kvh + kh) * page_size + off) * vd;
@@ -95,7 +105,12 @@ paged_attention_generic_kernel(const TA* __restrict__ q, const TA* __restrict__ 
     __syncthreads();
   }
   TA* orow = out + ((size_t)t * heads + h) * vd;
-  const float inv_l = 1.0f / l;
+  float inv_l = 1.0f / l;
+  if (sink) {          // one more term, exp(0 - max), in the denominator
+    const float top = fmaxf(m, 0.f);
+    const float c = expf(m - top);
+    inv_l = c / (l * c + expf(-top));
+  }
 #pragma unroll
   for (int i = 0; i < ATT_MAX_DPT; ++i) {
     const int d = threadIdx.x + i * ATT_THREADS;
@@ -112,13 +127,13 @@ IX_API int ix_paged_attention_generic(const void* q, const void* k_cache, const 
                                       const int* positions, void* out, int act_dtype, int T,
                                       int heads, int kvh, int hd, int vd, int page_size,
                                       int max_blocks, int window, float scale, float softcap,
-                                      cudaStream_t stream) {
+                                      int keep_first, int sink, cudaStream_t stream) {
   if (T <= 0) return IX_OK;
   if (heads <= 0 || kvh <= 0 || heads % kvh != 0 || page_size <= 0 || max_blocks <= 0)
     return IX_ERR_SIZE;
   if (hd <= 0 || hd > ATT_THREADS * ATT_MAX_DPT) return IX_ERR_SIZE;
   if (vd <= 0 || vd > ATT_THREADS * ATT_MAX_DPT) return IX_ERR_SIZE;   // values of another size
-  if (window < 0) return IX_ERR_SIZE;
+  if (window < 0 || keep_first < 0) return IX_ERR_SIZE;
   const size_t smem = (size_t)(hd + ATT_TILE) * sizeof(float);
   if (heads > 65535) return IX_ERR_SIZE;
   dim3 grid(T, heads);
@@ -126,6 +141,6 @@ IX_API int ix_paged_attention_generic(const void* q, const void* k_cache, const 
                     (paged_attention_generic_kernel<TA><<<grid, ATT_THREADS, smem, stream>>>(
                         (const TA*)q, (const TA*)k_cache, (const TA*)v_cache, block_table,
                         seq_of_token, positions, (TA*)out, heads, kvh, hd, vd, page_size,
-                        max_blocks, window, scale, softcap)));
+                        max_blocks, window, scale, softcap, keep_first, sink)));
   return ix_launch_status();
 }

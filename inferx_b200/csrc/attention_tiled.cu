@@ -12,6 +12,10 @@
 // maximum and sum are updated once per tile, so what a query computes does not depend
 // on how its sequence was cut into portions or on what else is in the batch.
 //
+// With `keep_first` > 0 the sequence's first keep_first keys stay visible beside the
+// window: their tiles (also at multiples of 64) are walked before the window's.  With
+// `sink` one is added to the softmax's denominator.
+//
 // Takes any element type, head sizes that are a multiple of 4 up to 256, any page size.
 #include "common.cuh"
 
@@ -51,7 +55,7 @@ paged_attention_tiled_kernel(const TA* __restrict__ q, const TA* __restrict__ kc
                              const int* __restrict__ cu_q, const int* __restrict__ q_pos0,
                              TA* __restrict__ out, int S, int heads, int kvh, int hd, int vd,
                              int page_size, int max_blocks, int window, float scale,
-                             float softcap) {
+                             float softcap, int keep_first, int sink) {
   extern __shared__ __align__(16) float tsm[];
   const int ld = hd + 4;                         // row pitch: 16-byte rows, no bank conflicts
   const int ldv = vd + 4;                        // the values' size may differ from the keys'
@@ -106,13 +110,18 @@ paged_attention_tiled_kernel(const TA* __restrict__ q, const TA* __restrict__ kc
 #pragma unroll
       for (int c = 0; c < 4; ++c) acc[i][j][c] = 0.f;
 
-  for (int kv0 = kv_lo & ~(TA_BK - 1); kv0 < kv_hi; kv0 += TA_BK) {
+  const int kv_lo_tile = kv_lo & ~(TA_BK - 1);
+  // keys below `kept` are visible to every query of the tile although the window has
+  // passed them; their tiles come first, then the walk jumps to the window's first tile
+  const int kept = window > 0 ? min(keep_first, kv_lo) : 0;
+  for (int kv0 = kept > 0 ? 0 : kv_lo_tile; kv0 < kv_hi;
+       kv0 = (kv0 + TA_BK >= kept && kv0 + TA_BK < kv_lo_tile) ? kv_lo_tile : kv0 + TA_BK) {
     __syncthreads();                             // the previous tile has been used
     for (int idx = tid; idx < TA_BK * chunks; idx += TA_THREADS) {
       const int r = idx / chunks, c = idx - r * chunks;
       const int kp = kv0 + r;
       float4 kv4 = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (kp >= kv_lo && kp < kv_hi) {
+      if ((kp >= kv_lo || kp < kept) && kp < kv_hi) {
         const int page = bt[kp / page_size];
         if (page >= 0) {
           const size_t row = (((size_t)page * kvh + kh) * page_size + kp % page_size) * hd;
@@ -125,7 +134,7 @@ paged_attention_tiled_kernel(const TA* __restrict__ q, const TA* __restrict__ kc
       const int r = idx / vchunks, c = idx - r * vchunks;
       const int kp = kv0 + r;
       float4 vv4 = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (kp >= kv_lo && kp < kv_hi) {
+      if ((kp >= kv_lo || kp < kept) && kp < kv_hi) {
         const int page = bt[kp / page_size];
         if (page >= 0) {
           const size_t row = (((size_t)page * kvh + kh) * page_size + kp % page_size) * vd;
@@ -169,7 +178,7 @@ paged_attention_tiled_kernel(const TA* __restrict__ q, const TA* __restrict__ kc
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int kp = kv0 + sk + 16 * j;
-        const bool seen = r < rows_valid && kp <= qp && kp >= first;
+        const bool seen = r < rows_valid && kp <= qp && (kp >= first || kp < keep_first);
         float sv = sc[i][j] * scale;
         if (softcap > 0.f) sv = softcap * tanhf(sv / softcap);   // squashed scores
         sc[i][j] = seen ? sv : -INFINITY;
@@ -232,7 +241,12 @@ paged_attention_tiled_kernel(const TA* __restrict__ q, const TA* __restrict__ kc
   for (int i = 0; i < 4; ++i) {
     const int r = 4 * ow + i;
     if (r >= rows_valid) continue;
-    const float inv_l = 1.0f / l_run[r];
+    float inv_l = 1.0f / l_run[r];
+    if (sink) {        // one more term, exp(0 - max), in the denominator
+      const float top = fmaxf(m_run[r], 0.f);
+      const float c = expf(m_run[r] - top);
+      inv_l = c / (l_run[r] * c + expf(-top));
+    }
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
       const int d = 4 * ol + 128 * j;
@@ -253,10 +267,11 @@ IX_API int ix_paged_attention_tiled(const void* q, const void* k_cache, const vo
                                     const int* block_table, const int* cu_q, const int* q_pos0,
                                     void* out, int act_dtype, int T, int S, int heads, int kvh,
                                     int hd, int vd, int page_size, int max_blocks, int window,
-                                    float scale, float softcap, cudaStream_t stream) {
+                                    float scale, float softcap, int keep_first, int sink,
+                                    cudaStream_t stream) {
   if (T <= 0) return IX_OK;
   if (S <= 0 || heads <= 0 || kvh <= 0 || heads % kvh != 0 || page_size <= 0 || max_blocks <= 0 ||
-      window < 0)
+      window < 0 || keep_first < 0)
     return IX_ERR_SIZE;
   if (!ix_paged_attention_tiled_applies(hd) || !ix_paged_attention_tiled_applies(vd))
     return IX_ERR_UNSUPPORTED;
@@ -278,7 +293,7 @@ IX_API int ix_paged_attention_tiled(const void* q, const void* k_cache, const vo
     kern<<<grid, TA_THREADS, smem, stream>>>((const TA*)q, (const TA*)k_cache, (const TA*)v_cache,
                                              block_table, cu_q, q_pos0, (TA*)out, S, heads, kvh,
                                              hd, vd, page_size, max_blocks, window, scale,
-                                             softcap);
+                                             softcap, keep_first, sink);
   });
   return ix_launch_status();
 }

@@ -68,12 +68,112 @@ __device__ __forceinline__ void select_topk(float* p, int E, int k, int renorm, 
   }
 }
 
+// How the chosen experts are picked and weighted beyond the plain top-k: `correction`
+// ([E] or null) is added to the scores for the choice alone; with `groups` > 0 the E
+// outputs form that many equal groups of neighbours, a group's value is its largest
+// corrected score, and only outputs of the `keep` groups with the largest values can be
+// chosen (ties to the lower group); `renorm_eps` >= 0 divides the chosen scores by (their
+// sum + renorm_eps).  `active` 0: the plain rule above.
+struct RouteRule {
+  const float* correction;
+  int groups;
+  int keep;
+  float renorm_eps;
+  int active;
+};
+
+#define ROUTER_MAX_GROUPS 32
+
+// (value, index) maximum over a warp; ties to the lower index; index 0x7fffffff: nothing
+__device__ __forceinline__ void warp_argmax(float& best, int& bi) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (oi != 0x7fffffff && (bi == 0x7fffffff || ob > best || (ob == best && oi < bi))) {
+      best = ob;
+      bi = oi;
+    }
+  }
+}
+
+// The ruled selection by one warp: p[0..E) holds logits and is overwritten.  Ties go to
+// the lower index, as in the plain selection.
+__device__ __forceinline__ void select_topk_ruled(float* p, int E, int k, int renorm, float scale,
+                                                  const RouteRule& rule, float* __restrict__ out_w,
+                                                  int* __restrict__ out_i, int lane) {
+  float mx = -INFINITY;
+  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, p[e]);
+  mx = warp_max(mx);
+  float sum = 0.f;
+  for (int e = lane; e < E; e += 32) {
+    const float v = expf(p[e] - mx);
+    p[e] = v;
+    sum += v;
+  }
+  sum = warp_sum(sum);
+  __syncwarp();
+  for (int e = lane; e < E; e += 32) p[e] = p[e] / sum;       // the scores
+  __syncwarp();
+  // groups that may be chosen from, as a mask over at most 32 groups (lane g owns group g)
+  unsigned allowed = 0xffffffffu;
+  const int gsize = rule.groups > 0 ? E / rule.groups : E;
+  if (rule.groups > 0) {
+    float gv = -INFINITY;
+    if (lane < rule.groups)
+      for (int e = lane * gsize; e < (lane + 1) * gsize; ++e)
+        gv = fmaxf(gv, p[e] + (rule.correction ? rule.correction[e] : 0.f));
+    allowed = 0u;
+    for (int r = 0; r < rule.keep; ++r) {
+      const bool open = lane < rule.groups && !((allowed >> lane) & 1u);
+      float best = open ? gv : -INFINITY;
+      int bi = open ? lane : 0x7fffffff;
+      warp_argmax(best, bi);
+      if (bi < 32) allowed |= 1u << bi;
+    }
+  }
+  float total = 0.f, my_w = 0.f;
+  int my_i = 0;
+  for (int s = 0; s < k; ++s) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float v = p[e];
+      if (v < 0.f || !((allowed >> (rule.groups > 0 ? e / gsize : 0)) & 1u)) continue;
+      const float c = v + (rule.correction ? rule.correction[e] : 0.f);
+      if (bi == 0x7fffffff || c > best) { best = c; bi = e; }
+    }
+    warp_argmax(best, bi);
+    const float prob = bi < E ? p[bi] : 0.f;
+    if (lane == s) { my_w = prob; my_i = bi < E ? bi : 0; }
+    total += prob;
+    __syncwarp();
+    if (lane == 0 && bi < E) p[bi] = -1.f;   // taken: below every score
+    __syncwarp();
+  }
+  if (lane < k) {
+    float wv = my_w;
+    if (rule.renorm_eps >= 0.f) wv = wv / (total + rule.renorm_eps);
+    else if (renorm && total > 0.f) wv = wv / total;
+    wv *= scale;
+    out_w[lane] = wv;
+    out_i[lane] = my_i;
+  }
+}
+
+__device__ __forceinline__ void select_by_rule(float* p, int E, int k, int renorm, float scale,
+                                               const RouteRule& rule, float* __restrict__ out_w,
+                                               int* __restrict__ out_i, int lane) {
+  if (rule.active) select_topk_ruled(p, E, k, renorm, scale, rule, out_w, out_i, lane);
+  else select_topk(p, E, k, renorm, scale, out_w, out_i, lane);
+}
+
 template <typename TA, int TOK>
 __global__ void __launch_bounds__(ROUTER_THREADS)
 router_topk_kernel(const TA* __restrict__ x, const float* __restrict__ w,
                    const float* __restrict__ extra_w, int T, int H, int E, int k, int renorm,
                    float scale, float* __restrict__ topk_w, int* __restrict__ topk_idx,
-                   float* __restrict__ extra_out) {
+                   float* __restrict__ extra_out, RouteRule rule) {
   extern __shared__ float smem[];
   float* xs = smem;                         // [TOK][H]
   float* lg = smem + (size_t)TOK * H;       // [TOK][E]
@@ -111,15 +211,15 @@ router_topk_kernel(const TA* __restrict__ x, const float* __restrict__ w,
   for (int tk = warp; tk < TOK; tk += nwarps) {
     const int t = t0 + tk;
     if (t >= T) continue;
-    select_topk(lg + tk * E, E, k, renorm, scale, topk_w + (size_t)t * k, topk_idx + (size_t)t * k,
-                lane);
+    select_by_rule(lg + tk * E, E, k, renorm, scale, rule, topk_w + (size_t)t * k,
+                   topk_idx + (size_t)t * k, lane);
   }
 }
 
 template <typename TA, int TOK>
 static int launch_router(const void* x, const float* w, const float* extra_w, int T, int H, int E,
                          int k, int renorm, float scale, float* topk_w, int* topk_idx,
-                         float* extra_out, cudaStream_t stream) {
+                         float* extra_out, RouteRule rule, cudaStream_t stream) {
   const size_t smem = ((size_t)TOK * H + (size_t)TOK * E) * sizeof(float);
   if (smem > 200 * 1024) return IX_ERR_SMEM;
   auto kern = router_topk_kernel<TA, TOK>;
@@ -130,7 +230,7 @@ static int launch_router(const void* x, const float* w, const float* extra_w, in
   }
   const int blocks = (T + TOK - 1) / TOK;
   kern<<<blocks, ROUTER_THREADS, smem, stream>>>((const TA*)x, w, extra_w, T, H, E, k, renorm,
-                                                 scale, topk_w, topk_idx, extra_out);
+                                                 scale, topk_w, topk_idx, extra_out, rule);
   return ix_launch_status();
 }
 
@@ -164,7 +264,8 @@ __global__ void __launch_bounds__(ROUTER_VTHREADS)
 router_topk_bf16_vec_kernel(const bf16* __restrict__ x, const float* __restrict__ w,
                             const float* __restrict__ extra_w, int T, int H, int E, int k,
                             int renorm, float scale, float* __restrict__ topk_w,
-                            int* __restrict__ topk_idx, float* __restrict__ extra_out) {
+                            int* __restrict__ topk_idx, float* __restrict__ extra_out,
+                            RouteRule rule) {
   extern __shared__ __align__(16) unsigned char rsm[];
   const int chunks = H >> 3;
   uint4* xs = reinterpret_cast<uint4*>(rsm);                               // [VTOK][chunks]
@@ -243,15 +344,15 @@ router_topk_bf16_vec_kernel(const bf16* __restrict__ x, const float* __restrict_
   for (int tk = warp; tk < ROUTER_VTOK; tk += nwarps) {
     const int t = t0 + tk;
     if (t >= T) continue;
-    select_topk(lg + tk * E, E, k, renorm, scale, topk_w + (size_t)t * k, topk_idx + (size_t)t * k,
-                lane);
+    select_by_rule(lg + tk * E, E, k, renorm, scale, rule, topk_w + (size_t)t * k,
+                   topk_idx + (size_t)t * k, lane);
   }
 }
 
 template <int VTOK, bool WIDE>
 static int launch_router_vec(const void* x, const float* w, const float* extra_w, int T, int H,
                              int E, int k, int renorm, float scale, float* topk_w, int* topk_idx,
-                             float* extra_out, cudaStream_t stream) {
+                             float* extra_out, RouteRule rule, cudaStream_t stream) {
   const size_t smem = (size_t)VTOK * (H / 8) * (WIDE ? 32 : 16) + (size_t)VTOK * E * sizeof(float);
   auto kern = router_topk_bf16_vec_kernel<VTOK, WIDE>;
   if (smem > 48 * 1024) {
@@ -260,7 +361,7 @@ static int launch_router_vec(const void* x, const float* w, const float* extra_w
     if (e2 != cudaSuccess) return (int)e2;
   }
   kern<<<(T + VTOK - 1) / VTOK, ROUTER_VTHREADS, smem, stream>>>(
-      (const bf16*)x, w, extra_w, T, H, E, k, renorm, scale, topk_w, topk_idx, extra_out);
+      (const bf16*)x, w, extra_w, T, H, E, k, renorm, scale, topk_w, topk_idx, extra_out, rule);
   return ix_launch_status();
 }
 
@@ -318,13 +419,14 @@ router_logits_kernel(const TA* __restrict__ x, const float* __restrict__ w,
 
 __global__ void __launch_bounds__(32)
 router_select_kernel(const float* __restrict__ logits, int E, int k, int renorm, float scale,
-                     float* __restrict__ topk_w, int* __restrict__ topk_idx) {
+                     float* __restrict__ topk_w, int* __restrict__ topk_idx, RouteRule rule) {
   extern __shared__ float prob[];
   IX_PDL_WAIT();
   const int t = blockIdx.x, lane = threadIdx.x;
   for (int e = lane; e < E; e += 32) prob[e] = logits[(size_t)t * E + e];
   __syncwarp();
-  select_topk(prob, E, k, renorm, scale, topk_w + (size_t)t * k, topk_idx + (size_t)t * k, lane);
+  select_by_rule(prob, E, k, renorm, scale, rule, topk_w + (size_t)t * k,
+                 topk_idx + (size_t)t * k, lane);
 }
 
 // Sizes beyond which the router and dispatch kernels refuse a call; a model is checked
@@ -332,10 +434,41 @@ router_select_kernel(const float* __restrict__ logits, int E, int k, int renorm,
 IX_API int ix_router_max_topk() { return ROUTER_MAX_TOPK; }
 IX_API int ix_router_max_experts() { return ROUTER_MAX_EXPERTS; }
 
+IX_API int ix_router_max_groups() { return ROUTER_MAX_GROUPS; }
+
+static int router_topk_impl(const void* x, const float* w, const float* extra_w, int act_dtype,
+                            int T, int H, int E, int k, int renorm, float scale, float* topk_w,
+                            int* topk_idx, float* extra_out, float* logits_scratch,
+                            RouteRule rule, cudaStream_t stream);
+
 IX_API int ix_router_topk(const void* x, const float* w, const float* extra_w, int act_dtype,
                           int T, int H, int E, int k, int renorm, float scale, float* topk_w,
                           int* topk_idx, float* extra_out, float* logits_scratch,
                           cudaStream_t stream) {
+  RouteRule rule = {nullptr, 0, 0, -1.f, 0};
+  return router_topk_impl(x, w, extra_w, act_dtype, T, H, E, k, renorm, scale, topk_w, topk_idx,
+                          extra_out, logits_scratch, rule, stream);
+}
+
+// The same with the choice ruled by a correction, groups and a division by (sum + eps).
+IX_API int ix_router_topk_ruled(const void* x, const float* w, const float* extra_w,
+                                int act_dtype, int T, int H, int E, int k, int renorm,
+                                float scale, const float* correction, int groups, int keep,
+                                float renorm_eps, float* topk_w, int* topk_idx, float* extra_out,
+                                float* logits_scratch, cudaStream_t stream) {
+  if (groups < 0 || groups > ROUTER_MAX_GROUPS) return IX_ERR_SIZE;
+  if (groups > 0 && (E % groups != 0 || keep <= 0 || keep > groups ||
+                     (long long)keep * (E / groups) < k))
+    return IX_ERR_SIZE;
+  RouteRule rule = {correction, groups, keep, renorm_eps, 1};
+  return router_topk_impl(x, w, extra_w, act_dtype, T, H, E, k, renorm, scale, topk_w, topk_idx,
+                          extra_out, logits_scratch, rule, stream);
+}
+
+static int router_topk_impl(const void* x, const float* w, const float* extra_w, int act_dtype,
+                            int T, int H, int E, int k, int renorm, float scale, float* topk_w,
+                            int* topk_idx, float* extra_out, float* logits_scratch,
+                            RouteRule rule, cudaStream_t stream) {
   if (T <= 0) return IX_OK;
   if (H <= 0 || E <= 0 || k <= 0 || k > E || k > ROUTER_MAX_TOPK) return IX_ERR_SIZE;
   if (extra_w && !extra_out) return IX_ERR_SIZE;
@@ -351,7 +484,7 @@ IX_API int ix_router_topk(const void* x, const float* w, const float* extra_w, i
       int rc = ix_launch_status();
       if (rc != 0) return rc;
       ix_launch(router_select_kernel, dim3(T), dim3(32), (size_t)E * sizeof(float), stream,
-                (const float*)logits_scratch, E, k, renorm, scale, topk_w, topk_idx);
+                (const float*)logits_scratch, E, k, renorm, scale, topk_w, topk_idx, rule);
       return ix_launch_status();
     }
     IX_DISPATCH_DTYPE(act_dtype, TA,
@@ -361,7 +494,7 @@ IX_API int ix_router_topk(const void* x, const float* w, const float* extra_w, i
     int rc = ix_launch_status();
     if (rc != 0) return rc;
     ix_launch(router_select_kernel, dim3(T), dim3(32), (size_t)E * sizeof(float), stream,
-              (const float*)logits_scratch, E, k, renorm, scale, topk_w, topk_idx);
+              (const float*)logits_scratch, E, k, renorm, scale, topk_w, topk_idx, rule);
     return ix_launch_status();
   }
   if (vec) {
@@ -387,9 +520,9 @@ IX_API int ix_router_topk(const void* x, const float* w, const float* extra_w, i
 #define IX_ROUTER_CASE(V)                                                                       \
   case V:                                                                                       \
     return wide ? launch_router_vec<V, true>(x, w, extra_w, T, H, E, k, renorm, scale, topk_w,  \
-                                             topk_idx, extra_out, stream)                       \
+                                             topk_idx, extra_out, rule, stream)                 \
                 : launch_router_vec<V, false>(x, w, extra_w, T, H, E, k, renorm, scale, topk_w, \
-                                              topk_idx, extra_out, stream);
+                                              topk_idx, extra_out, rule, stream);
       switch (vtok) {
         IX_ROUTER_CASE(4)
         IX_ROUTER_CASE(8)
@@ -408,15 +541,15 @@ IX_API int ix_router_topk(const void* x, const float* w, const float* extra_w, i
   IX_DISPATCH_DTYPE(act_dtype, TA, {
     if (tok == 8)
       return launch_router<TA, 8>(x, w, extra_w, T, H, E, k, renorm, scale, topk_w, topk_idx,
-                                  extra_out, stream);
+                                  extra_out, rule, stream);
     if (tok == 4)
       return launch_router<TA, 4>(x, w, extra_w, T, H, E, k, renorm, scale, topk_w, topk_idx,
-                                  extra_out, stream);
+                                  extra_out, rule, stream);
     if (tok == 2)
       return launch_router<TA, 2>(x, w, extra_w, T, H, E, k, renorm, scale, topk_w, topk_idx,
-                                  extra_out, stream);
+                                  extra_out, rule, stream);
     return launch_router<TA, 1>(x, w, extra_w, T, H, E, k, renorm, scale, topk_w, topk_idx,
-                                extra_out, stream);
+                                extra_out, rule, stream);
   });
   return IX_OK;
 }

@@ -148,6 +148,13 @@ def check_router_limits(hidden: int, num_experts: int, top_k: int, where: str = 
         raise KernelError(f"{where}: {top_k} experts per token of {num_experts}")
 
 
+def check_router_group_limits(group_count: int, where: str = ""):
+    most = _lib().ix_router_max_groups()
+    if group_count > most:
+        raise KernelError(f"{where}: {group_count} router groups exceed the selection "
+                          f"kernel's limit of {most}")
+
+
 def embed(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None,
           scale: float = 1.0):
     """out[t] = table[ids[t]] * scale, widened to fp32 (the residual stream)."""
@@ -389,7 +396,7 @@ def qkv_project_rope_append(x: torch.Tensor, w: torch.Tensor, bias: Optional[tor
 def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                             block_table: torch.Tensor, seq_of_token: torch.Tensor,
                             positions: torch.Tensor, window: int, scale: float,
-                            softcap: float = 0.0):
+                            softcap: float = 0.0, keep_first: int = 0, sink: bool = False):
     _chk("q", q)
     _chk("k_cache", k_cache, q.dtype)
     _chk("v_cache", v_cache, q.dtype)
@@ -405,7 +412,8 @@ def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
     code = _lib().ix_paged_attention_generic(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(seq_of_token),
         _ptr(positions), _ptr(out), _dtype_code(q), T, heads, kvh, hd, vd, page,
-        block_table.shape[1], window, ctypes.c_float(scale), ctypes.c_float(softcap), _stream())
+        block_table.shape[1], window, ctypes.c_float(scale), ctypes.c_float(softcap),
+        int(keep_first), 1 if sink else 0, _stream())
     _check(code, "paged_attention_generic")
     _count()
     return out
@@ -413,7 +421,8 @@ def paged_attention_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
 
 def paged_attention_tiled(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                           block_table: torch.Tensor, cu_q: torch.Tensor, q_pos0: torch.Tensor,
-                          window: int, scale: float, softcap: float = 0.0):
+                          window: int, scale: float, softcap: float = 0.0, keep_first: int = 0,
+                          sink: bool = False):
     """CUDA-core attention for a ragged batch, tiled (32 queries of a sequence against 64
     keys at a time in shared memory, fp32 math): sequence s brings the queries
     q[cu_q[s]:cu_q[s+1]] at positions q_pos0[s], q_pos0[s]+1, ...  Any element type, head
@@ -437,7 +446,8 @@ def paged_attention_tiled(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch
     code = _lib().ix_paged_attention_tiled(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(cu_q), _ptr(q_pos0),
         _ptr(out), _dtype_code(q), T, S, heads, kvh, hd, vd, page, block_table.shape[1], window,
-        ctypes.c_float(scale), ctypes.c_float(softcap), _stream())
+        ctypes.c_float(scale), ctypes.c_float(softcap), int(keep_first), 1 if sink else 0,
+        _stream())
     _check(code, "paged_attention_tiled")
     _count()
     return out
@@ -456,9 +466,16 @@ ROUTER_FEW_TOKENS = 128
 
 
 def router_topk(x: torch.Tensor, w: torch.Tensor, top_k: int, renormalize: bool, scale: float,
-                extra_w: Optional[torch.Tensor] = None
+                extra_w: Optional[torch.Tensor] = None,
+                correction: Optional[torch.Tensor] = None, group_count: int = 0,
+                group_keep: int = 0, renorm_eps: Optional[float] = None
                 ) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
     """fp32 router logits, softmax over all experts, top-k (ties to the lower index).
+
+    ``correction`` (fp32 [E]) is added to the scores for the choice alone; with
+    ``group_count`` > 0 the outputs form that many equal groups of neighbours and only
+    outputs of the ``group_keep`` groups with the largest corrected score can be chosen;
+    ``renorm_eps`` >= 0 divides the chosen scores by (their sum + renorm_eps).
 
     Returns (weights [T,k] fp32, experts [T,k] int32, x.extra_w [T] fp32 or None).
     Few tokens: one warp per (token, expert) computes the logits and one warp per
@@ -476,9 +493,22 @@ def router_topk(x: torch.Tensor, w: torch.Tensor, top_k: int, renormalize: bool,
     ex = torch.empty((T,), dtype=torch.float32, device=x.device) if extra_w is not None else None
     few = T < ROUTER_FEW_TOKENS   # few tokens: logits by many blocks, then a selection kernel
     scratch = torch.empty((T, E), dtype=torch.float32, device=x.device) if few else None
-    code = _lib().ix_router_topk(_ptr(x), _ptr(w), _ptr(extra_w), _dtype_code(x), T, H, E, top_k,
-                                 1 if renormalize else 0, ctypes.c_float(scale), _ptr(tw),
-                                 _ptr(ti), _ptr(ex), _ptr(scratch), _stream())
+    ruled = (correction is not None or group_count > 0
+             or (renorm_eps is not None and renorm_eps >= 0))
+    if ruled:
+        _chk("correction", correction, torch.float32, optional=True)
+        if correction is not None and correction.numel() != E:
+            raise KernelError("router_topk: one correction per router output")
+        code = _lib().ix_router_topk_ruled(
+            _ptr(x), _ptr(w), _ptr(extra_w), _dtype_code(x), T, H, E, top_k,
+            1 if renormalize else 0, ctypes.c_float(scale), _ptr(correction), int(group_count),
+            int(group_keep), ctypes.c_float(-1.0 if renorm_eps is None else renorm_eps),
+            _ptr(tw), _ptr(ti), _ptr(ex), _ptr(scratch), _stream())
+    else:
+        code = _lib().ix_router_topk(
+            _ptr(x), _ptr(w), _ptr(extra_w), _dtype_code(x), T, H, E, top_k,
+            1 if renormalize else 0, ctypes.c_float(scale), _ptr(tw), _ptr(ti), _ptr(ex),
+            _ptr(scratch), _stream())
     _check(code, "router_topk")
     _count(2 if few else 1)
     return tw, ti, ex
@@ -784,8 +814,11 @@ def paged_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
 
 def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                     block_table: torch.Tensor, step, window: int, scale: float,
-                    softcap: float = 0.0, fp32_weights: bool = False):
-    """Causal attention of this step's queries over the paged cache.  With ``softcap``
+                    softcap: float = 0.0, fp32_weights: bool = False, keep_first: int = 0,
+                    sink: bool = False):
+    """Causal attention of this step's queries over the paged cache.  ``keep_first``: with
+    a window, the sequence's first tokens stay visible beside it; ``sink``: one is added
+    to the softmax's denominator (both run on the fp32-arithmetic kernels).  With ``softcap``
     > 0 a score s becomes softcap * tanh(s / softcap) before the softmax.  With
     ``fp32_weights``, or value pages whose head size differs from the keys', the
     fp32-arithmetic kernels run whatever the element type.
@@ -796,9 +829,9 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     tuned kernels do not take, to the general kernel."""
     hd = q.shape[2]
     page = k_cache.shape[2]
-    if fp32_weights or v_cache.shape[3] != hd:
+    if fp32_weights or v_cache.shape[3] != hd or sink or (keep_first and window > 0):
         return _paged_attention_softcap(q, k_cache, v_cache, block_table, step, window, scale,
-                                        softcap)
+                                        softcap, keep_first if window > 0 else 0, sink)
     if softcap > 0 and not (scale > 0 and USE_TMA_DECODE and _tma_decode_applies(q, page)
                             and USE_TCGEN05_ATTENTION and _tc_prefill_applies(q, page)):
         # of the tuned kernels only the TMA decode form and the tcgen05 prompt form squash
@@ -828,7 +861,8 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
 def paged_attention_decode_any(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                                block_table: torch.Tensor, kv_len: torch.Tensor, max_kv_len: int,
                                window: int, scale: float, softcap: float = 0.0,
-                               splits: Optional[int] = None):
+                               splits: Optional[int] = None, keep_first: int = 0,
+                               sink: bool = False):
     """Split-KV attention in fp32 arithmetic for a batch in which sequence s brings the one
     query q[s] at position kv_len[s] - 1: any head size up to 512, value heads of a size
     of their own, any element type.  Returns [S, heads, value size]."""
@@ -856,7 +890,7 @@ def paged_attention_decode_any(q: torch.Tensor, k_cache: torch.Tensor, v_cache: 
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(kv_len), _ptr(part_o),
         _ptr(part_ml), _ptr(out), _dtype_code(q), S, heads, kvh, hd, vd, page,
         block_table.shape[1], window, ctypes.c_float(scale), ctypes.c_float(softcap), splits,
-        _stream()), "paged_attention_decode_any")
+        int(keep_first), 1 if sink else 0, _stream()), "paged_attention_decode_any")
     _count(2 if splits > 1 else 1)
     return out
 
@@ -866,22 +900,24 @@ def paged_attention_decode_any(q: torch.Tensor, k_cache: torch.Tensor, v_cache: 
 DECODE_ANY_MIN_KEYS = 128
 
 
-def _paged_attention_softcap(q, k_cache, v_cache, block_table, step, window, scale, softcap):
+def _paged_attention_softcap(q, k_cache, v_cache, block_table, step, window, scale, softcap,
+                             keep_first=0, sink=False):
     """The fp32-arithmetic kernels (squashed scores or not)."""
     hd = q.shape[2]
     if (getattr(step, "all_decode", False) and getattr(step, "kv_len", None) is not None
             and step.num_tokens == step.num_seqs and step.max_kv_len >= DECODE_ANY_MIN_KEYS
             and max(hd, v_cache.shape[3]) <= 512):
         return paged_attention_decode_any(q, k_cache, v_cache, block_table, step.kv_len,
-                                          step.max_kv_len, window, scale, softcap)
+                                          step.max_kv_len, window, scale, softcap,
+                                          keep_first=keep_first, sink=sink)
     if (step.num_tokens >= TILED_ATTENTION_MIN_QUERIES * step.num_seqs
             and _lib().ix_paged_attention_tiled_applies(hd)
             and _lib().ix_paged_attention_tiled_applies(v_cache.shape[3])
             and getattr(step, "cu_q", None) is not None):
         return paged_attention_tiled(q, k_cache, v_cache, block_table, step.cu_q, step.q_pos0,
-                                     window, scale, softcap)
+                                     window, scale, softcap, keep_first, sink)
     return paged_attention_generic(q, k_cache, v_cache, block_table, step.seq_of_token,
-                                   step.positions, window, scale, softcap)
+                                   step.positions, window, scale, softcap, keep_first, sink)
 
 
 USE_TCGEN05 = True           # prompt-sized grouped products go to the tcgen05 kernel
@@ -1848,3 +1884,129 @@ def check_delta_limits(dim: int, taps: int, where: str = ""):
     if not 1 <= taps <= 16:
         raise KernelError(f"{where}: a convolution of {taps} taps is not one the kernel takes "
                           "(1 to 16)")
+
+
+def embed_pair_norm(table: torch.Tensor, pair_table: torch.Tensor, gain: torch.Tensor, step,
+                    prev_state: torch.Tensor, buckets: int, mul_prev: int, mul_cur: int,
+                    eps: float):
+    """fp32 [T, H]: rmsnorm(table[token] + pair_table[row]) * gain with row = (previous *
+    mul_prev + token * mul_cur) mod buckets, row ``buckets`` at position 0.  The previous
+    token of a sequence's first token in this step comes from ``prev_state`` (int32
+    [slots, 1]), which then takes the sequence's last token of the step."""
+    _chk("table", table)
+    _chk("pair_table", pair_table, table.dtype)
+    _chk("gain", gain, torch.float32)
+    _chk("prev_state", prev_state, torch.int32)
+    V, H = table.shape
+    if pair_table.shape != (buckets + 1, H) or gain.numel() != H:
+        raise KernelError("embed_pair_norm: the pair table must be [buckets + 1, width] and "
+                          "the gain [width]")
+    T = step.token_ids.numel()
+    out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    _check(_lib().ix_embed_pair_norm(
+        _ptr(table), _ptr(pair_table), _dtype_code(table), _ptr(gain), _ptr(step.token_ids),
+        _ptr(step.positions), _ptr(step.seq_of_token), _ptr(step.cu_q), _ptr(step.state_slot),
+        _ptr(prev_state), _ptr(out), T, H, ctypes.c_longlong(buckets),
+        ctypes.c_longlong(mul_prev), ctypes.c_longlong(mul_cur), ctypes.c_float(eps),
+        _stream()), "embed_pair_norm")
+    _count()
+    return out
+
+
+def attention_prepare(qkv: torch.Tensor, positions: torch.Tensor, freq: Optional[torch.Tensor],
+                      magnitude: float, rotary_dim: int, interleaved: bool, heads: int,
+                      kv_heads: int, head_dim: int, value_dim: int,
+                      q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor], eps: float,
+                      head_unit: bool, earlier: Optional[torch.Tensor],
+                      lam: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
+                      v_cache: Optional[torch.Tensor], slots: Optional[torch.Tensor],
+                      want_dense_kv: bool = False):
+    """Prepares a step's q, k and v rows (``qkv`` [T, q | k | v], a view with unit inner
+    stride) for attention, per token and in fp32: with gains, the RMS norm of the whole q
+    row and of the whole k row; the rotation of the first ``rotary_dim`` entries of every
+    q and k head by position * ``freq`` (pairs are neighbours when ``interleaved``, else
+    half a rotation apart; cos and sin times ``magnitude``); with ``head_unit`` every q
+    and k head divided by its root mean square; with ``earlier`` ([T, kv_heads *
+    value_dim], a view) the values become (1 - lam) v + lam earlier.  Returns q [T, heads,
+    head_dim]; writes k and v into the pages at ``slots`` (and returns them densely when
+    asked)."""
+    _chk("positions", positions, torch.int32)
+    _chk("freq", freq, torch.float32, optional=True)
+    _chk("q_gain", q_gain, torch.float32, optional=True)
+    _chk("k_gain", k_gain, torch.float32, optional=True)
+    _chk("lam", lam, torch.float32, optional=True)
+    _chk("slots", slots, torch.int32, optional=True)
+    dq, dk, dv = heads * head_dim, kv_heads * head_dim, kv_heads * value_dim
+    ld = _row_view("attention_prepare: qkv", qkv, dq + dk + dv)
+    T = qkv.shape[0]
+    ld_e = 0
+    if earlier is not None:
+        if earlier.dtype != qkv.dtype or earlier.shape[0] != T or lam is None:
+            raise KernelError("attention_prepare: the earlier values must match the rows, and "
+                              "need their weight")
+        ld_e = _row_view("attention_prepare: earlier", earlier, dv)
+    if rotary_dim and (freq is None or freq.numel() != rotary_dim // 2):
+        raise KernelError("attention_prepare: freq must have rotary_dim / 2 entries")
+    if (q_gain is None) != (k_gain is None) or (
+            q_gain is not None and (q_gain.numel() != dq or k_gain.numel() != dk)):
+        raise KernelError("attention_prepare: one gain per q entry and per k entry")
+    page_size = 1
+    if k_cache is not None:
+        _chk("k_cache", k_cache, qkv.dtype)
+        _chk("v_cache", v_cache, qkv.dtype)
+        if slots is None or slots.numel() != T:
+            raise KernelError("attention_prepare: a cache needs one slot per token")
+        P, ckv, page_size, chd = k_cache.shape
+        if ckv != kv_heads or chd != head_dim or \
+                tuple(v_cache.shape) != (P, ckv, page_size, value_dim):
+            raise KernelError("attention_prepare: cache geometry does not match the heads")
+    q = torch.empty((T, heads, head_dim), dtype=qkv.dtype, device=qkv.device)
+    k = v = None
+    if want_dense_kv:
+        k = torch.empty((T, kv_heads, head_dim), dtype=qkv.dtype, device=qkv.device)
+        v = torch.empty((T, kv_heads, value_dim), dtype=qkv.dtype, device=qkv.device)
+    _check(_lib().ix_attention_prepare(
+        _ptr(qkv), ctypes.c_longlong(ld), _dtype_code(qkv), _ptr(positions), _ptr(freq),
+        ctypes.c_float(magnitude), int(rotary_dim), 1 if interleaved else 0, heads, kv_heads,
+        head_dim, value_dim, _ptr(q_gain), _ptr(k_gain), ctypes.c_float(eps),
+        1 if head_unit else 0, _ptr(earlier), ctypes.c_longlong(ld_e), _ptr(lam), _ptr(slots),
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), page_size, _ptr(k), _ptr(v), T, _stream()),
+        "attention_prepare")
+    _count()
+    return (q, k, v) if want_dense_kv else q
+
+
+def glu_bias_act(gu: torch.Tensor, bias: Optional[torch.Tensor], activation: str = "gelu_tanh"):
+    """act(g + b_g) * (u + b_u) for rows laid out g | u (``bias`` fp32 [2 I] laid out the
+    same way, or None); ``activation`` "gelu_tanh" or "silu"."""
+    _chk("gu", gu)
+    _chk("bias", bias, torch.float32, optional=True)
+    if activation not in ("gelu_tanh", "silu"):
+        raise KernelError(f"glu_bias_act: no activation {activation!r}")
+    T, two_i = gu.shape
+    if two_i % 2 or (bias is not None and bias.numel() != two_i):
+        raise KernelError("glu_bias_act: rows are gate | up, with one bias entry each")
+    out = torch.empty((T, two_i // 2), dtype=gu.dtype, device=gu.device)
+    _check(_lib().ix_glu_bias_act(_ptr(gu), _ptr(bias), _ptr(out), _dtype_code(gu), T,
+                                  two_i // 2, 1 if activation == "silu" else 0, _stream()),
+           "glu_bias_act")
+    _count()
+    return out
+
+
+def identity_rows(x: torch.Tensor, rows: torch.Tensor, offsets: torch.Tensor,
+                  first_identity: int, y: torch.Tensor):
+    """y[r] = x[rows[r]] for the grouped rows of the router's outputs from
+    ``first_identity`` on (experts that return their input); ``offsets`` has one entry per
+    router output plus one."""
+    _chk("x", x)
+    _chk("y", y, x.dtype)
+    _chk("rows", rows, torch.int32)
+    _chk("offsets", offsets, torch.int32)
+    if y.shape[1] != x.shape[1] or y.shape[0] != rows.numel():
+        raise KernelError("identity_rows: y must hold one row of x's width per grouped row")
+    _check(_lib().ix_identity_rows(_ptr(x), _ptr(rows), _ptr(offsets), int(first_identity),
+                                   offsets.numel() - 1, _ptr(y), _dtype_code(x), rows.numel(),
+                                   x.shape[1], _stream()), "identity_rows")
+    _count()
+    return y

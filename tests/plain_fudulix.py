@@ -175,7 +175,9 @@ def attend(q, k, v, scale, size, keep_first, sink):
 
 
 def mix_values(v, v_first, lam):
-    return v if v_first is None else (1.0 - lam) * v + lam * v_first
+    """Entry by entry over a token's values (layers that mix have as many of them, however
+    they split them into heads)."""
+    return v if v_first is None else (1.0 - lam) * v + lam * v_first.reshape(v.shape)
 
 
 def attention(h, weights, p, m, eps, positions, v_first, store=ident):

@@ -89,7 +89,8 @@ def test_rejections(tiny_a, change, match):
 def test_unknown_architecture_lists_the_known_ones(tiny_a):
     with pytest.raises(ConfigError, match="Qwen2MoeForCausalLM"):
         config_from_json(dict(tiny_a, architectures=["MysteryForCausalLM"]))
-    assert known_architectures() == ["Mapovik", "Qwen2MoeForCausalLM", "Tinapel", "Zuzisun"]
+    assert known_architectures() == ["Fudulix", "Mapovik", "Qwen2MoeForCausalLM", "Tinapel",
+                                     "Zuzisun"]
 
 
 def test_registry_takes_another_architecture(tiny_a):
