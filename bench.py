@@ -21,7 +21,9 @@ live requests) over its time, against the measured copy bandwidth.
 size (``--design-sizes 1k,2k,4k``) with the prompt and decode throughput of the Zuzisun
 design beside Qwen2-MoE with every layer dense at equal sizes; ``--design tinapel`` does the
 same for the Tinapel design beside Qwen2-MoE with the same experts (``--design-pattern``
-names the mixers of its layers).
+names the mixers of its layers), ``--design mapovik`` for the Mapovik design beside Tinapel,
+and ``--design fudulix`` for the Fudulix design beside Qwen2-MoE with the same heads, window
+and experts.
 
 A decode step's working set (gigabytes of weights and cache) is far larger than the
 126 MB L2, so nothing stays resident between timed iterations.
@@ -895,6 +897,57 @@ def mapovik_configs(z, layers, pattern):
     return new, twin
 
 
+# `--designs --design fudulix`: the Fudulix design (windowed attention with prepared q, k
+# and v in two kinds, a gated unit with biases, a mixture whose router knows groups, a
+# correction and identity experts) beside Qwen2-MoE at equal width, depth, heads, key/value
+# heads, head size, window, experts and feed-forward widths.  Layers alternate: the second
+# kind with the dense unit, the first kind with the mixture; the twin's even layers are dense
+# and its odd ones sparse, all of them with the same window.
+FUDULIX_SIZES = {
+    # heads of 128 (keys and values) over `kv` key/value heads; `experts` router outputs of
+    # which two return their input, in 4 groups of which 2 are kept
+    "1k": dict(width=1024, heads=8, kv=2, experts=16, top=2, ff=512, shared=2048),
+    "2k": dict(width=2048, heads=16, kv=4, experts=32, top=4, ff=1024, shared=4096),
+    "4k": dict(width=4096, heads=32, kv=8, experts=32, top=4, ff=1408, shared=5632),
+}
+FUDULIX_WINDOW = 1024
+
+
+def fudulix_configs(z, layers):
+    import math
+    W, win = z["width"], FUDULIX_WINDOW
+    scale = 1.0 / math.sqrt(128.0)
+    second = {"type": "attention_2", "mixer": {
+        "heads": z["heads"], "kv_heads": z["kv"], "dim": 128, "vdim": 128, "scale": scale,
+        "conv": 4, "mask": {"size": win, "keep_first": 4}, "v_mix": True,
+        "rot": {"dims": 128, "base": 1000000.0,
+                "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}},
+        "mlp": {"kind": "dense", "ff": z["shared"]}}
+    first = {"type": "attention", "mixer": {
+        "heads": z["heads"], "kv_heads": z["kv"], "dim": 128, "vdim": 128, "scale": scale,
+        "mask": {"size": win}, "v_mix": True,
+        "rot": {"dims": 64, "base": 10000.0,
+                "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 2048}}},
+        "mlp": {"kind": "moe", "expert": {"ff": z["ff"]},
+                "router": {"experts": z["experts"] - 2, "identity": 2, "top": z["top"],
+                           "groups": {"count": 4, "keep": 2}},
+                "shared": {"ff": z["shared"]}}}
+    new = {"architecture": "Fudulix", "vocab": DESIGN_VOCAB, "width": W, "norm": {"eps": 1e-6},
+           "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}},
+           "layers": [(second, first)[i % 2] for i in range(layers)]}
+    twin = {"architectures": ["Qwen2MoeForCausalLM"], "model_type": "qwen2_moe",
+            "num_hidden_layers": layers, "hidden_size": W,
+            "num_attention_heads": z["heads"], "num_key_value_heads": z["kv"],
+            "head_dim": 128, "num_experts": z["experts"], "num_experts_per_tok": z["top"],
+            "moe_intermediate_size": z["ff"], "shared_expert_intermediate_size": z["shared"],
+            "intermediate_size": z["shared"], "decoder_sparse_step": 1,
+            "mlp_only_layers": list(range(0, layers, 2)), "norm_topk_prob": True,
+            "vocab_size": DESIGN_VOCAB, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
+            "use_sliding_window": True, "sliding_window": win, "max_window_layers": 0,
+            "tie_word_embeddings": True, "torch_dtype": "bfloat16"}
+    return new, twin
+
+
 def designs(args):
     """One JSON line per size: prompt tokens/s (one prompt of --prefill-tokens, default
     2048) and decode tokens/s (--batch sequences at --context) of both designs, device
@@ -905,16 +958,21 @@ def designs(args):
     B = args.batch
     tinapel = args.design == "tinapel"
     mapovik = args.design == "mapovik"
-    sizes = MAPOVIK_SIZES if mapovik else TINAPEL_SIZES if tinapel else DESIGN_SIZES
-    first, second = (("mapovik", "tinapel") if mapovik else ("tinapel", "qwen2_moe") if tinapel
-                     else ("zuzisun", "qwen2_dense"))
+    fudulix = args.design == "fudulix"
+    sizes = (FUDULIX_SIZES if fudulix else MAPOVIK_SIZES if mapovik
+             else TINAPEL_SIZES if tinapel else DESIGN_SIZES)
+    first, second = (("fudulix", "qwen2_moe") if fudulix else ("mapovik", "tinapel") if mapovik
+                     else ("tinapel", "qwen2_moe") if tinapel else ("zuzisun", "qwen2_dense"))
     for name in (args.design_sizes.split(",") if args.design_sizes else list(sizes)):
         z = sizes[name]
         C = args.context or 4096
         row = {"size": name, "layers": layers, "width": z["width"], "heads": z["heads"],
                "ff": z["ff"], "prompt_tokens": prompt, "batch": B,
                "context": C, "dtype": "bf16", "data": "synthetic, random weights"}
-        if mapovik:
+        if fudulix:
+            row["window"] = FUDULIX_WINDOW
+            pair = fudulix_configs(z, layers)
+        elif mapovik:
             pattern = (args.design_pattern if "wkv" not in args.design_pattern
                        else "parallel,delta,delta,parallel").split(",")
             row["pattern"] = pattern
@@ -991,7 +1049,7 @@ def main(argv=None):
                          "beside the closest Qwen2-MoE at equal sizes (random weights); --layers (4), "
                          "--batch, --context (4096), --prefill-tokens (2048) apply")
     ap.add_argument("--design-sizes", default="", help="with --designs: of 1k,2k,4k (all)")
-    ap.add_argument("--design", default="zuzisun", choices=["zuzisun", "tinapel", "mapovik"],
+    ap.add_argument("--design", default="zuzisun", choices=["zuzisun", "tinapel", "mapovik", "fudulix"],
                     help="with --designs: which design stands beside its closest model")
     ap.add_argument("--design-pattern", default="wkv,gla,attention,attention",
                     help="with --design tinapel: the mixers of the layers, repeated; with "

@@ -41,7 +41,7 @@ class FudulixMixer:
     dim: int
     vdim: int
     scale: float
-    window: int               # mask.size: a query sees itself and the window - 1 before it
+    window: int               # mask.size: a query sees itself and the window - 1 before it; 0: all
     keep_first: int = 0       # attention_2: the first tokens stay visible
     conv: int = 0             # attention_2: taps of the convolutions after the projections
     v_mix: bool = False
@@ -124,7 +124,7 @@ class FudulixConfig:
             m, at = layer.mixer, f"layers[{i}].mixer"
             need(min(m.heads, m.kv_heads, m.dim, m.vdim) > 0 and m.heads % m.kv_heads == 0,
                  f"{at}: {m.heads} heads of {m.dim} / {m.vdim} over {m.kv_heads} key/value heads")
-            need(m.window > 0, f"{at}.mask: size {m.window} must be positive")
+            need(m.window >= 0, f"{at}.mask: size {m.window} must not be negative")
             need(m.keep_first >= 0 and m.conv >= 0, f"{at}: keep_first {m.keep_first}, conv {m.conv}")
             if m.rot is not None:
                 need(0 <= m.rot.dims <= m.dim and m.rot.dims % 2 == 0 and m.rot.base > 0,
@@ -169,9 +169,11 @@ class FudulixConfig:
         for layer in self.layers:
             m = layer.mixer
             mixer = {"heads": m.heads, "kv_heads": m.kv_heads, "dim": m.dim, "vdim": m.vdim,
-                     "scale": m.scale, "mask": {"size": m.window}, "v_mix": m.v_mix}
+                     "scale": m.scale, "mask": {"size": m.window} if m.window else {},
+                     "v_mix": m.v_mix}
             if layer.type == ATTENTION_2:
-                mixer["mask"]["keep_first"] = m.keep_first
+                if m.window:
+                    mixer["mask"]["keep_first"] = m.keep_first
                 mixer["conv"] = m.conv
             if m.rot is not None:
                 rot = {"dims": m.rot.dims, "base": m.rot.base}
@@ -219,12 +221,12 @@ def _layer(obj, where) -> FudulixLayer:
                           f"(known: {ATTENTION!r}, {ATTENTION_2!r})")
     at = f"{where}.mixer"
     m = _Reader(_object(obj, "mixer", where), at)
-    mask = _Reader(_object(m.obj, "mask", at), f"{at}.mask")
+    mask = _Reader(_object(m.obj, "mask", at, default={}), f"{at}.mask")
     heads, dim = m.integer("heads"), m.integer("dim")
     second = kind == ATTENTION_2
     mixer = FudulixMixer(
         heads=heads, kv_heads=m.integer("kv_heads", heads), dim=dim, vdim=m.integer("vdim", dim),
-        scale=m.number("scale"), window=mask.integer("size"),
+        scale=m.number("scale"), window=mask.integer("size", 0),
         keep_first=mask.integer("keep_first", 0) if second else 0,
         conv=m.integer("conv", 0) if second else 0, v_mix=m.boolean("v_mix", False),
         rot=_rotation(m.obj, kind, at))

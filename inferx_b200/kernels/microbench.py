@@ -14,6 +14,7 @@
     python -m inferx_b200.kernels.microbench recurrent --tokens 4096 --batch 1 --hidden 2048 --head-dim 64
     python -m inferx_b200.kernels.microbench recurrent --tokens 64 --batch 64 --hidden 2048 --head-dim 64
     python -m inferx_b200.kernels.microbench attn_prefill --tokens 2048 --softcap 30
+    python -m inferx_b200.kernels.microbench prepared --tokens 2048 --hidden 2048 --heads 16 --kv-heads 4 --inter 4096 --experts 32 --batch 8 --window 1024
 
 Each case runs one kernel face at Qwen1.5-MoE-A2.7B sizes (or the sizes given),
 cycling through enough copies of its inputs that consecutive iterations do not
@@ -489,10 +490,133 @@ def delta(args):
     return out
 
 
+def prepared(args):
+    """The kernels of the decoders with prepared attention, each beside the like kernel of
+    the Qwen2-MoE path at the same sizes: ``--tokens`` rows of ``--hidden``, ``--heads``
+    over ``--kv-heads`` heads of ``--head-dim`` (keys and values), a feed-forward of
+    ``--inter``, ``--experts`` router outputs of which ``--top-k`` are chosen; attention of
+    one prompt of ``--tokens`` tokens, and of ``--batch`` single tokens at ``--context``,
+    over a window of ``--window`` (1024 when not given).  GB/s over the bytes the operation
+    has to move; attention also as GFLOP/s of its two products."""
+    from . import ops
+    T, W, I = args.tokens, args.hidden, args.inter
+    H, G, D = args.heads, args.kv_heads, args.head_dim
+    E, K = args.experts, args.top_k
+    win = args.window or 1024
+    dt = torch.bfloat16
+    dev = "cuda"
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    n = max(2, min(8, _copies(T * W * 8)))
+    vocab, buckets = 32000, 65521
+    table = torch.randn(vocab, W, device=dev, dtype=dt)
+    pairs = torch.randn(buckets + 1, W, device=dev, dtype=dt)
+    gain = torch.ones(W, device=dev)
+    ids = [torch.randint(0, vocab, (T,), device=dev, dtype=torch.int32) for _ in range(n)]
+    step = types.SimpleNamespace(
+        cu_q=i32([0, T]), seq_of_token=torch.zeros(T, dtype=torch.int32, device=dev),
+        state_slot=i32([0]), positions=torch.arange(T, dtype=torch.int32, device=dev),
+        q_pos0=i32([0]), token_ids=ids[0], num_seqs=1, num_tokens=T)
+    prev = torch.zeros(2, 1, dtype=torch.int32, device=dev)
+
+    def embed_pair(i):
+        step.token_ids = ids[i]
+        ops.embed_pair_norm(table, pairs, gain, step, prev, buckets, 31, 7, 1e-6)
+    dq, dk = H * D, G * D
+    row = dq + 2 * dk
+    qkv = [torch.randn(T, row, device=dev, dtype=dt) for _ in range(n)]
+    page = args.page
+    P = -(-T // page) + 1
+    kc = torch.zeros(P, G, page, D, device=dev, dtype=dt)
+    vc = torch.zeros(P, G, page, D, device=dev, dtype=dt)
+    slots = torch.arange(T, dtype=torch.int32, device=dev)
+    freq = torch.rand(D // 2, device=dev)
+    qg, kg = torch.ones(dq, device=dev), torch.ones(dk, device=dev)
+    lam = torch.tensor([0.3], device=dev)
+    earlier = [torch.randn(T, dk, device=dev, dtype=dt) for _ in range(n)]
+    gu = [torch.randn(T, 2 * I, device=dev, dtype=dt) for _ in range(n)]
+    bias = torch.randn(2 * I, device=dev)
+    x = [torch.randn(T, W, device=dev, dtype=dt) for _ in range(n)]
+    rw = torch.randn(E, W, device=dev) * 0.05
+    corr = torch.randn(E, device=dev) * 0.1
+    groups = 4 if E % 4 == 0 else 1
+    keep = 2 if groups == 4 and 2 * (E // 4) >= K else groups
+    cases = {
+        "embed_pair_norm": (embed_pair, T * W * (2 + 2 + 4)),
+        "embed (like)": (lambda i: ops.embed(table, ids[i]), T * W * (2 + 4)),
+        "attention_prepare (projection norm, half rotation, blend)": (
+            lambda i: ops.attention_prepare(qkv[i], step.positions, freq, 1.1, D, False, H, G, D,
+                                            D, qg, kg, 1e-6, False, earlier[i], lam, kc, vc,
+                                            slots), T * (2 * row * 2 + dk * 2)),
+        "attention_prepare (pair rotation, unit heads)": (
+            lambda i: ops.attention_prepare(qkv[i], step.positions, freq[:D // 4].contiguous(),
+                                            1.0, D // 2, True, H, G, D, D, None, None, 1e-6, True,
+                                            None, None, kc, vc, slots), T * 2 * row * 2),
+        "qkv_rope_append (like)": (
+            lambda i: ops.qkv_rope_append(qkv[i], None, step.positions, freq, D, H, G, D, kc, vc,
+                                          slots), T * 2 * row * 2),
+        "glu_bias_act (gelu_tanh, biases)": (lambda i: ops.glu_bias_act(gu[i], bias, "gelu_tanh"),
+                                             6 * T * I),
+        "silu_mul (like)": (lambda i: ops.silu_mul(gu[i]), 6 * T * I),
+        "router_topk (correction, groups, sum + eps)": (
+            lambda i: ops.router_topk(x[i], rw, K, True, 1.0, correction=corr, group_count=groups,
+                                      group_keep=keep, renorm_eps=1e-20), T * W * 2),
+        "router_topk (like)": (lambda i: ops.router_topk(x[i], rw, K, True, 1.0), T * W * 2),
+    }
+    out = {"case": "prepared", "tokens": T, "hidden": W, "inter": I, "heads": H, "kv_heads": G,
+           "head_dim": D, "experts": E, "top_k": K, "window": win}
+    for name, (fn, nbytes) in cases.items():
+        us = _time(fn, n, args.iters)
+        out[name] = {"us": round(us, 2), "GBps": round(nbytes / us / 1e3, 1)}
+    # attention: one prompt of T tokens over the window; B single tokens at the context
+    scale = 1.0 / math.sqrt(D)
+    pages = -(-T // page)
+    kp = torch.randn(pages, G, page, D, device=dev, dtype=dt) * 0.3
+    vp = torch.randn(pages, G, page, D, device=dev, dtype=dt)
+    bt = torch.arange(pages, dtype=torch.int32, device=dev).view(1, pages)
+    q = torch.randn(T, H, D, device=dev, dtype=dt) * 0.3
+    seen = sum(min(p + 1, win) for p in range(T))
+    flops = 4.0 * H * D * seen
+    prompt = {
+        "tiled fp32 weights, kept first keys, sink": lambda i: ops.paged_attention_tiled(
+            q, kp, vp, bt, step.cu_q, step.q_pos0, win, scale, 0.0, 4, True),
+        "tiled fp32 weights": lambda i: ops.paged_attention_tiled(
+            q, kp, vp, bt, step.cu_q, step.q_pos0, win, scale),
+        "tcgen05 (like)": lambda i: ops.paged_attention_prefill(
+            q, kp, vp, bt, step.cu_q, step.q_pos0, win, scale, max_kv_len=T),
+    }
+    for name, fn in prompt.items():
+        us = _time(fn, 1, max(3, args.iters // 10))
+        out[f"prompt attention: {name}"] = {"us": round(us, 1),
+                                            "GFLOPs": round(flops / us / 1e3, 1)}
+    B, C = args.batch, args.context
+    per_seq = -(-C // page)
+    nc = min(_copies(B * min(C, win) * G * D * 4), 8)
+    kcs = [torch.randn(B * per_seq, G, page, D, device=dev, dtype=dt) * 0.3 for _ in range(nc)]
+    vcs = [torch.randn(B * per_seq, G, page, D, device=dev, dtype=dt) for _ in range(nc)]
+    btd = torch.randperm(B * per_seq, device=dev).to(torch.int32).view(B, per_seq)
+    qd = torch.randn(B, H, D, device=dev, dtype=dt) * 0.3
+    kv_len = torch.full((B,), C, dtype=torch.int32, device=dev)
+    nbytes = B * min(C, win) * G * D * 2 * 2
+    single = {
+        "any-size fp32 weights, kept first keys, sink": lambda i: ops.paged_attention_decode_any(
+            qd, kcs[i], vcs[i], btd, kv_len, C, win, scale, keep_first=4, sink=True),
+        "any-size fp32 weights": lambda i: ops.paged_attention_decode_any(
+            qd, kcs[i], vcs[i], btd, kv_len, C, win, scale),
+        "TMA (like)": lambda i: ops.paged_attention_decode(qd, kcs[i], vcs[i], btd, kv_len, C,
+                                                           win, scale),
+    }
+    for name, fn in single.items():
+        us = _time(fn, nc, args.iters)
+        out[f"single-token attention: {name}"] = {"us": round(us, 2),
+                                                  "GBps": round(nbytes / us / 1e3, 1)}
+    return out
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("case", choices=["attn_decode", "grouped", "dense", "attn_prefill", "router",
-                                     "qkv", "latent_attn", "rowwise", "recurrent", "delta"])
+                                     "qkv", "latent_attn", "rowwise", "recurrent", "delta",
+                                     "prepared"])
     ap.add_argument("--softcap", type=float, default=0.0,
                     help="attn_decode, attn_prefill: squash scores to softcap * tanh(s / softcap)")
     ap.add_argument("--rank", type=int, default=512, help="latent_attn: entries of the latent")

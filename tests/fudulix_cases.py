@@ -156,3 +156,33 @@ def bound_for(dtype, model_dir, requests):
     if dtype == "float32":
         return _bound(model_dir, requests, plain.round_f32, 3.0, 3e-5)
     return _bound(model_dir, requests, plain.round_bf16, 3.0, 5e-3)
+
+
+def decisive_rows(model_dir, requests, least=1e-3):
+    """{(request, position)} whose logits cannot have been changed by a router's close
+    call: no router of this or an earlier token of the request chose with a margin below
+    ``least``, neither in the plain model nor in the plain model that rounds what it stores
+    to bfloat16 (a choice that rounding can turn changes the token's stream, and through
+    the keys and values every later token's).  Tests of bfloat16 runs compare these rows;
+    the 32-bit runs compare all."""
+    cfg, w = plain.read_model_folder(model_dir)
+    keep = set()
+    for rid, toks in requests.items():
+        exact, rounded = [], []
+        plain.forward(cfg, w, toks, margins=exact)
+        plain.forward(cfg, w, toks, store=plain.round_bf16, margins=rounded)
+        for p, (a, b) in enumerate(zip(exact, rounded)):
+            if min(a, b) < least:
+                break
+            keep.add((rid, p))
+    return keep
+
+
+def rows_to_compare(dtype, model_dir, requests, rows, share=0.25):
+    """The produced rows a run in ``dtype`` is held to (see ``decisive_rows``)."""
+    if dtype == "float32":
+        return rows
+    keep = decisive_rows(model_dir, requests)
+    kept = {k: v for k, v in rows.items() if k in keep}
+    assert len(kept) >= share * len(rows), "too many close calls: the test compares too little"
+    return kept

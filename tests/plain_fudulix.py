@@ -261,7 +261,35 @@ def choose(scores, correction, top, group_count, group_keep):
     return idx, w / (w.sum() + 1e-20)
 
 
-def moe_ff(h, weights, p, f, store=ident):
+def choice_margin(scores, correction, top, group_count, group_keep, stake=1e-3):
+    """How far the choice is from another one that would matter: the smaller of the
+    distance between the last kept group and the first one left out and the distance
+    between the last chosen output and the first one left out.  A pair whose outputs all
+    have scores below ``stake`` does not count (swapping them moves next to no weight), nor
+    does a side with nothing left out; then the margin is infinite."""
+    n = scores.numel()
+    pick = scores + correction
+    size = n // group_count
+    groups = sorted(range(group_count),
+                    key=lambda g: (-float(pick[g * size:(g + 1) * size].max()), g))
+    kept = groups[:group_keep]
+    margin = math.inf
+    if group_keep < group_count:
+        last, first_out = groups[group_keep - 1], groups[group_keep]
+        at_stake = max(float(scores[g * size:(g + 1) * size].max()) for g in (last, first_out))
+        if at_stake >= stake:
+            margin = float(pick[last * size:(last + 1) * size].max()
+                           - pick[first_out * size:(first_out + 1) * size].max())
+    allowed = sorted((i for i in range(n) if i // size in kept),
+                     key=lambda i: (-float(pick[i]), i))
+    if top < len(allowed):
+        last, first_out = allowed[top - 1], allowed[top]
+        if max(float(scores[last]), float(scores[first_out])) >= stake:
+            margin = min(margin, float(pick[last] - pick[first_out]))
+    return margin
+
+
+def moe_ff(h, weights, p, f, store=ident, margins=None):
     r = f["router"]
     experts, identity = r["experts"], r.get("identity", 0)
     groups = r.get("groups") or {"count": 1, "keep": 1}
@@ -270,6 +298,9 @@ def moe_ff(h, weights, p, f, store=ident):
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         idx, w = choose(scores[t], corr, r["top"], groups["count"], groups["keep"])
+        if margins is not None:
+            margins[t] = min(margins[t], choice_margin(scores[t], corr, r["top"],
+                                                       groups["count"], groups["keep"]))
         for e, we in zip(idx, w):
             if e >= experts:
                 out[t] += we * h[t]
@@ -281,8 +312,12 @@ def moe_ff(h, weights, p, f, store=ident):
 
 
 # -- the model -----------------------------------------------------------------------
-def forward(cfg, weights, tokens, store=ident, layers_out=None):
+def forward(cfg, weights, tokens, store=ident, layers_out=None, margins=None):
+    """Logits [T, vocab].  ``layers_out`` (a list) receives the stream after every layer;
+    ``margins`` (a list) receives, per token, the smallest ``choice_margin`` of its routers."""
     eps = cfg["norm"]["eps"]
+    if margins is not None:
+        margins[:] = [math.inf] * len(tokens)
     positions = list(range(len(tokens)))
     x = embed(cfg, weights, tokens)
     v_first = None
@@ -300,7 +335,7 @@ def forward(cfg, weights, tokens, store=ident, layers_out=None):
         if f is not None:
             h = store(rms_norm(x, _w(weights, f"{p}.norm2"), eps))
             y = dense_ff(h, weights, f"{p}.mlp", store) if f["kind"] == "dense" else \
-                moe_ff(h, weights, f"{p}.mlp", f, store)
+                moe_ff(h, weights, f"{p}.mlp", f, store, margins)
             x = x + store(y)
         if layers_out is not None:
             layers_out.append(x.clone())

@@ -75,7 +75,7 @@ def test_config_without_optional_parts():
     (lambda c: c["layers"][0]["mixer"].update(kv_heads=3), "key/value heads"),
     (lambda c: c["layers"][0]["mixer"]["rot"].update(dims=7), "rotated entries"),
     (lambda c: c["layers"][0]["mixer"]["rot"].update(dims=26), "rotated entries"),
-    (lambda c: c["layers"][0]["mixer"]["mask"].update(size=0), "must be positive"),
+    (lambda c: c["layers"][0]["mixer"]["mask"].update(size=-1), "must not be negative"),
     (lambda c: c["layers"][1]["mixer"].update(vdim=8), "cannot be mixed"),
     (lambda c: c["layers"][1]["mlp"]["router"].update(top=7), "identity experts"),
     (lambda c: c["layers"][1]["mlp"]["router"]["groups"].update(count=4), "groups"),
