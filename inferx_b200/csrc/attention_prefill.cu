@@ -274,6 +274,247 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc,
   }
 }
 
+// The same walk with the softmax weights kept to 16 bits in their product with the values
+// (each weight enters as its bfloat16 rounding plus the bfloat16 rounding of the rest, two
+// tensor-core products into the same fp32 accumulator), value heads of a size of their own
+// (64 or 128 each), optionally the sequence's first `keep_first` keys visible beside the
+// window and one added to the softmax's denominator (`sink`).  For decoders that want their
+// attention weights in 32-bit arithmetic: the scores are exact products of bfloat16 numbers
+// summed in fp32, maxima, exponentials and sums are fp32, and the weights lose nothing a
+// bfloat16 value would not lose many times over.
+template <int HD, int VD>
+__global__ void __launch_bounds__(PF_THREADS)
+attn_prefill_exact_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc,
+                    const bf16* __restrict__ vc, const int* __restrict__ block_table,
+                    const int* __restrict__ cu_q, const int* __restrict__ q_pos0,
+                    bf16* __restrict__ out, int S, int heads, int kvh, int page_size,
+                    int page_shift, int maxb, int window, float scale_log2e,
+                          int keep_first, int sink) {
+  constexpr int CH = HD / 8;            // 16-byte chunks per row
+  constexpr int KS = HD / 16;           // k-steps of Q K^T
+  constexpr int CHV = VD / 8;           // 16-byte chunks per value row
+  constexpr int DT = VD / 8;            // n-tiles of the output
+  extern __shared__ __align__(128) unsigned char smem[];
+  unsigned char* Qs = smem;                               // [BM][HD]
+  unsigned char* Ks = Qs + PF_BM * HD * 2;                // [2][BN][HD]
+  unsigned char* Vs = Ks + 2 * PF_BN * HD * 2;            // [2][BN][VD]
+
+  // which sequence and which 64-query tile of it
+  // blocks are handed out in launch order; the tiles with the most keys to walk (the
+  // last queries of a sequence) come first, all heads of a tile together, so that the
+  // short tiles fill the end of the grid
+  int s = 0, tile = gridDim.y - 1 - blockIdx.y;
+  {
+    bool found = false;
+    for (int ss = 0; ss < S; ++ss) {
+      const int n = cu_q[ss + 1] - cu_q[ss];
+      const int tiles = (n + PF_BM - 1) / PF_BM;
+      if (tile < tiles) { s = ss; found = true; break; }
+      tile -= tiles;
+    }
+    if (!found) return;
+  }
+  const int h = blockIdx.x;
+  const int kh = h / (heads / kvh);
+  const int tok0 = cu_q[s];
+  const int nq = cu_q[s + 1] - tok0;
+  const int q0 = tile * PF_BM;
+  const int rows_valid = min(PF_BM, nq - q0);
+  const int pos0 = q_pos0[s] + q0;               // position of the tile's first query
+  const int pmax = pos0 + rows_valid - 1;
+  const int kv_lo = window > 0 ? max(0, pos0 - window + 1) : 0;
+  const int kv_hi = pmax + 1;
+  const int kt0 = (kv_lo / PF_BN) * PF_BN;
+  // keys below `kept` stay visible although the window has passed them: their tiles (those
+  // that end before the window's first tile) are walked first
+  const int kept = window > 0 ? min(keep_first, kv_lo) : 0;
+  const int n_kept = min((kept + PF_BN - 1) / PF_BN, kt0 / PF_BN);
+  const int n_tiles = n_kept + (kv_hi - kt0 + PF_BN - 1) / PF_BN;
+  auto tile_base = [&](int it) { return it < n_kept ? it * PF_BN : kt0 + (it - n_kept) * PF_BN; };
+  const int* bt = block_table + (size_t)s * maxb;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+
+  // Q tile -> shared
+  for (int idx = tid; idx < PF_BM * CH; idx += PF_THREADS) {
+    const int r = idx / CH, c = idx - r * CH;
+    const bool ok = r < rows_valid;
+    const bf16* src = q + ((size_t)(tok0 + q0 + (ok ? r : 0)) * heads + h) * HD + c * 8;
+    cp_async16(Qs + swz<CH>(r, c), src, ok);
+  }
+  auto load_kv = [&](int it, int stage) {
+    const int kbase = tile_base(it);
+    unsigned char* kd = Ks + stage * PF_BN * HD * 2;
+    unsigned char* vd = Vs + stage * PF_BN * VD * 2;
+    for (int idx = tid; idx < PF_BN * (CH + CHV); idx += PF_THREADS) {
+      const bool is_v = idx >= PF_BN * CH;
+      const int j = is_v ? idx - PF_BN * CH : idx;
+      const int r = is_v ? j / CHV : j / CH, c = is_v ? j - r * CHV : j - r * CH;
+      const int kp = kbase + r;
+      const bool ok = (kp >= kv_lo || kp < kept) && kp < kv_hi;
+      size_t row = 0;
+      if (ok) {
+        const int pi = page_shift >= 0 ? (kp >> page_shift) : (kp / page_size);
+        const int po = page_shift >= 0 ? (kp & (page_size - 1)) : (kp % page_size);
+        row = ((size_t)bt[pi] * kvh + kh) * page_size + po;
+      }
+      if (is_v) cp_async16(vd + swz<CHV>(r, c), vc + row * VD + c * 8, ok);
+      else cp_async16(kd + swz<CH>(r, c), kc + row * HD + c * 8, ok);
+    }
+  };
+  load_kv(0, 0);
+  cp_async_commit();
+
+  float o[DT][4];
+#pragma unroll
+  for (int j = 0; j < DT; ++j)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) o[j][c] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  unsigned qf[KS][4];
+  const int row_a = warp * 16 + g, row_b = row_a + 8;     // this thread's two query rows
+  const int pos_a = pos0 + row_a, pos_b = pos0 + row_b;
+
+  for (int it = 0; it < n_tiles; ++it) {
+    const int stage = it & 1;
+    if (it + 1 < n_tiles) load_kv(it + 1, stage ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    if (it == 0) {
+#pragma unroll
+      for (int kk = 0; kk < KS; ++kk) {
+        const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        const int c = kk * 2 + (lane >> 4);
+        ldmatrix_x4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], Qs + swz<CH>(r, c));
+      }
+    }
+    const unsigned char* kt = Ks + stage * PF_BN * HD * 2;
+    const unsigned char* vt = Vs + stage * PF_BN * VD * 2;
+    const int kbase = tile_base(it);
+
+    float sc[PF_BN / 8][4];
+#pragma unroll
+    for (int j = 0; j < PF_BN / 8; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) sc[j][c] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < KS; ++kk) {
+#pragma unroll
+      for (int j = 0; j < PF_BN / 8; j += 2) {
+        unsigned b0, b1, b2, b3;
+        const int r = (j + (lane >> 4)) * 8 + (lane & 7);
+        const int c = kk * 2 + ((lane >> 3) & 1);
+        ldmatrix_x4(b0, b1, b2, b3, kt + swz<CH>(r, c));
+        mma16816(sc[j], qf[kk], b0, b1);
+        mma16816(sc[j + 1], qf[kk], b2, b3);
+      }
+    }
+    // scale, mask by position, row max
+    const bool need_mask = (kbase + PF_BN - 1 > pos0) || (window > 0 && kbase < pmax - window + 1)
+                           || kbase < kv_lo || it < n_kept;
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < PF_BN / 8; ++j) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        float v = sc[j][c] * scale_log2e;
+        if (need_mask) {
+          const int kp = kbase + j * 8 + 2 * t + (c & 1);
+          const int pos = (c & 2) ? pos_b : pos_a;
+          const bool vis = kp <= pos && (window <= 0 || kp >= pos - window + 1 ||
+                                         kp < keep_first);
+          if (!vis) v = -INFINITY;
+        }
+        sc[j][c] = v;
+        mx[c >> 1] = fmaxf(mx[c >> 1], v);
+      }
+    }
+    float corr[2], m_use[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+      const float m_new = fmaxf(m_run[r], mx[r]);
+      m_use[r] = m_new == -INFINITY ? 0.f : m_new;
+      corr[r] = fast_exp2(m_run[r] - m_use[r]);
+      m_run[r] = m_new;
+      l_run[r] *= corr[r];
+    }
+#pragma unroll
+    for (int j = 0; j < DT; ++j) {
+      o[j][0] *= corr[0]; o[j][1] *= corr[0];
+      o[j][2] *= corr[1]; o[j][3] *= corr[1];
+    }
+    // a weight enters its product with the values as the sum of two bfloat16 numbers,
+    // its rounding and the rounding of what that left over: 16 bits of the weight
+    unsigned pf[PF_BN / 16][4], pl[PF_BN / 16][4];
+#pragma unroll
+    for (int j = 0; j < PF_BN / 8; ++j) {
+      const float p0 = fast_exp2(sc[j][0] - m_use[0]);
+      const float p1 = fast_exp2(sc[j][1] - m_use[0]);
+      const float p2 = fast_exp2(sc[j][2] - m_use[1]);
+      const float p3 = fast_exp2(sc[j][3] - m_use[1]);
+      l_run[0] += p0 + p1;
+      l_run[1] += p2 + p3;
+      const __nv_bfloat162 ha = __floats2bfloat162_rn(p0, p1), hb = __floats2bfloat162_rn(p2, p3);
+      const float2 fa = __bfloat1622float2(ha), fb = __bfloat1622float2(hb);
+      pf[j >> 1][(j & 1) * 2 + 0] = *reinterpret_cast<const unsigned*>(&ha);
+      pf[j >> 1][(j & 1) * 2 + 1] = *reinterpret_cast<const unsigned*>(&hb);
+      pl[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p0 - fa.x, p1 - fa.y);
+      pl[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2 - fb.x, p3 - fb.y);
+    }
+    // O += P V
+#pragma unroll
+    for (int kk = 0; kk < PF_BN / 16; ++kk) {
+#pragma unroll
+      for (int jd = 0; jd < DT; jd += 2) {
+        unsigned b0, b1, b2, b3;
+        const int r = kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+        const int c = jd + (lane >> 4);
+        ldmatrix_x4_trans(b0, b1, b2, b3, vt + swz<CHV>(r, c));
+        mma16816(o[jd], pf[kk], b0, b1);
+        mma16816(o[jd + 1], pf[kk], b2, b3);
+        mma16816(o[jd], pl[kk], b0, b1);
+        mma16816(o[jd + 1], pl[kk], b2, b3);
+      }
+    }
+    __syncthreads();   // everyone is done with this stage before it is refilled
+  }
+  cp_async_wait<0>();
+
+  // finish the row sums across the quad and write
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+  float inv_a = l_run[0] > 0.f ? 1.0f / l_run[0] : 0.f;
+  float inv_b = l_run[1] > 0.f ? 1.0f / l_run[1] : 0.f;
+  if (sink) {      // one more term in the denominator: 2^(0 - max), maxima being in log2 units
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      if (!(l_run[r] > 0.f)) continue;
+      const float top = fmaxf(m_run[r], 0.f);
+      const float c = fast_exp2(m_run[r] - top);
+      const float inv = c / (l_run[r] * c + fast_exp2(-top));
+      if (r == 0) inv_a = inv; else inv_b = inv;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < DT; ++j) {
+    const int d = j * 8 + 2 * t;
+    if (row_a < rows_valid) {
+      bf16* dst = out + ((size_t)(tok0 + q0 + row_a) * heads + h) * VD + d;
+      *reinterpret_cast<unsigned*>(dst) = pack_bf16(o[j][0] * inv_a, o[j][1] * inv_a);
+    }
+    if (row_b < rows_valid) {
+      bf16* dst = out + ((size_t)(tok0 + q0 + row_b) * heads + h) * VD + d;
+      *reinterpret_cast<unsigned*>(dst) = pack_bf16(o[j][2] * inv_b, o[j][3] * inv_b);
+    }
+  }
+}
+
 template <int HD>
 static int launch_prefill(const void* q, const void* kc, const void* vc, const int* bt,
                           const int* cu_q, const int* q_pos0, void* out, int T, int S, int heads,
@@ -317,5 +558,60 @@ IX_API int ix_paged_attention_prefill(const void* q, const void* k_cache, const 
   if (hd == 64)
     return launch_prefill<64>(q, k_cache, v_cache, block_table, cu_q, q_pos0, out, T, S, heads,
                               kvh, page_size, max_blocks, window, scale, stream);
+  return IX_ERR_UNSUPPORTED;
+}
+
+template <int HD, int VD>
+static int launch_prefill_exact(const void* q, const void* kc, const void* vc, const int* bt,
+                                const int* cu_q, const int* q_pos0, void* out, int T, int S,
+                                int heads, int kvh, int page_size, int maxb, int window,
+                                float scale, int keep_first, int sink, cudaStream_t stream) {
+  const size_t smem = (size_t)(PF_BM + 2 * PF_BN) * HD * 2 + (size_t)2 * PF_BN * VD * 2;
+  auto kern = attn_prefill_exact_kernel<HD, VD>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const int tiles = (T + PF_BM - 1) / PF_BM + S;
+  if (tiles > 65535) return IX_ERR_SIZE;
+  dim3 grid(heads, tiles);
+  int page_shift = -1;
+  if ((page_size & (page_size - 1)) == 0)
+    for (page_shift = 0; (1 << page_shift) < page_size; ++page_shift) {}
+  kern<<<grid, PF_THREADS, smem, stream>>>((const bf16*)q, (const bf16*)kc, (const bf16*)vc, bt,
+                                           cu_q, q_pos0, (bf16*)out, S, heads, kvh, page_size,
+                                           page_shift, maxb, window,
+                                           scale * 1.4426950408889634f, keep_first, sink);
+  return ix_launch_status();
+}
+
+IX_API int ix_paged_attention_prefill_exact_applies(int hd, int vd) {
+  return (hd == 64 || hd == 128) && (vd == 64 || vd == 128);
+}
+
+// q [T, heads, hd], out [T, heads, vd], caches [pages, kvh, page_size, hd or vd], bfloat16.
+IX_API int ix_paged_attention_prefill_exact(const void* q, const void* k_cache,
+                                            const void* v_cache, const int* block_table,
+                                            const int* cu_q, const int* q_pos0, void* out, int T,
+                                            int S, int heads, int kvh, int hd, int vd,
+                                            int page_size, int max_blocks, int window, float scale,
+                                            int keep_first, int sink, cudaStream_t stream) {
+  if (T <= 0 || S <= 0) return IX_OK;
+  if (heads <= 0 || kvh <= 0 || heads % kvh != 0 || page_size <= 0 || max_blocks <= 0 ||
+      window < 0 || keep_first < 0 || !(scale > 0.f))
+    return IX_ERR_SIZE;
+  if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15)
+    return IX_ERR_ALIGN;
+#define PF_EXACT(H_, V_)                                                                       \
+  if (hd == H_ && vd == V_)                                                                    \
+    return launch_prefill_exact<H_, V_>(q, k_cache, v_cache, block_table, cu_q, q_pos0, out, T, \
+                                        S, heads, kvh, page_size, max_blocks, window, scale,   \
+                                        keep_first, sink, stream);
+  PF_EXACT(64, 64)
+  PF_EXACT(64, 128)
+  PF_EXACT(128, 64)
+  PF_EXACT(128, 128)
+#undef PF_EXACT
   return IX_ERR_UNSUPPORTED;
 }

@@ -82,8 +82,10 @@ IX_API int ix_embed_pair_norm(const void* table, const void* pairs, int dtype, c
 
 // ---------------------------------------------------------------------------
 // One block per token.  The q and k parts of the row are held in shared memory as fp32
-// from the first read to the last write.
-template <typename TA>
+// from the first read to the last write.  VEC (bfloat16 rows whose parts start on 16-byte
+// marks and whose head sizes are multiples of 8): the row is read and everything is written
+// in 16-byte accesses; the arithmetic and its order are the same.
+template <typename TA, bool VEC>
 __global__ void __launch_bounds__(PP_THREADS)
 attention_prepare_kernel(const TA* __restrict__ qkv, long long ld, const int* __restrict__ positions,
                          const float* __restrict__ freq, float magnitude, int rot, int interleaved,
@@ -94,22 +96,61 @@ attention_prepare_kernel(const TA* __restrict__ qkv, long long ld, const int* __
                          TA* __restrict__ q_out, TA* __restrict__ k_cache,
                          TA* __restrict__ v_cache, int page_size, TA* __restrict__ k_dense,
                          TA* __restrict__ v_dense) {
-  extern __shared__ float row[];            // [dq + dk]
+  extern __shared__ float row[];            // [dq + dk], then cos and sin of the pairs [rot]
   __shared__ float scratch[32];
   IX_PDL_WAIT();
   const int t = blockIdx.x;
   const int dq = heads * hd, dk = kvh * hd, dv = kvh * vd;
   const TA* src = qkv + (size_t)t * ld;
   const int tid = threadIdx.x;
+  float* turn = row + dq + dk;              // cos of pair i, then sin of pair i
+  if (rot > 0) {                            // once per token: every head turns by the same angles
+    const float pos = (float)positions[t];
+    for (int i = tid; i < (rot >> 1); i += PP_THREADS) {
+      float sn, cs;
+      sincosf(pos * freq[i], &sn, &cs);
+      turn[i] = cs * magnitude;
+      turn[(rot >> 1) + i] = sn * magnitude;
+    }
+  }
   float sq = 0.f, sk = 0.f;
-  for (int i = tid; i < dq + dk; i += PP_THREADS) {
-    const float x = to_f32(src[i]);
-    row[i] = x;
-    if (i < dq) sq += x * x; else sk += x * x;
+  if constexpr (VEC) {
+    const uint4* src8 = reinterpret_cast<const uint4*>(src);
+    for (int c = tid; c < (dq + dk) >> 3; c += PP_THREADS) {
+      float x[8];
+      bf8_to_f32(src8[c], x);
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        row[8 * c + e] = x[e];
+        ss += x[e] * x[e];
+      }
+      if (8 * c < dq) sq += ss; else sk += ss;
+    }
+  } else {
+    for (int i = tid; i < dq + dk; i += PP_THREADS) {
+      const float x = to_f32(src[i]);
+      row[i] = x;
+      if (i < dq) sq += x * x; else sk += x * x;
+    }
   }
   if (q_gain) {
-    sq = block_sum(sq, scratch);
-    sk = block_sum(sk, scratch);
+    // both sums in one meeting of the block: warp w's pair sits at scratch[2 w], [2 w + 1]
+    {
+      const int lane = tid & 31, warp = tid >> 5;
+      sq = warp_sum(sq);
+      sk = warp_sum(sk);
+      if (lane == 0) {
+        scratch[2 * warp] = sq;
+        scratch[2 * warp + 1] = sk;
+      }
+      __syncthreads();
+      sq = sk = 0.f;
+      for (int w = 0; w < PP_THREADS / 32; ++w) {     // ascending warps: a fixed order
+        sq += scratch[2 * w];
+        sk += scratch[2 * w + 1];
+      }
+    }
     const float iq = 1.0f / sqrtf(sq / (float)dq + eps);
     const float ik = 1.0f / sqrtf(sk / (float)dk + eps);
     for (int i = tid; i < dq + dk; i += PP_THREADS)
@@ -118,13 +159,9 @@ attention_prepare_kernel(const TA* __restrict__ qkv, long long ld, const int* __
   __syncthreads();
   if (rot > 0) {
     const int half = rot >> 1;
-    const float pos = (float)positions[t];
     for (int idx = tid; idx < (heads + kvh) * half; idx += PP_THREADS) {
       const int h = idx / half, i = idx - h * half;
-      float sn, cs;
-      sincosf(pos * freq[i], &sn, &cs);
-      sn *= magnitude;
-      cs *= magnitude;
+      const float cs = turn[i], sn = turn[half + i];
       float* v = row + (size_t)h * hd;
       const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
       const float x = v[a], y = v[b];
@@ -147,9 +184,36 @@ attention_prepare_kernel(const TA* __restrict__ qkv, long long ld, const int* __
   }
   const int slot = slots ? slots[t] : -1;
   TA* qo = q_out + (size_t)t * dq;
-  for (int i = tid; i < dq; i += PP_THREADS) qo[i] = from_f32<TA>(row[i]);
   const bool cached = k_cache != nullptr && slot >= 0;
   const size_t page = cached ? slot / page_size : 0, off = cached ? slot % page_size : 0;
+  if constexpr (VEC) {
+    for (int c = tid; c < dq >> 3; c += PP_THREADS)
+      reinterpret_cast<uint4*>(qo)[c] = f32_to_bf8(row + 8 * c);
+    for (int c = tid; c < dk >> 3; c += PP_THREADS) {
+      const int i = 8 * c, kh = i / hd, d = i - kh * hd;
+      const uint4 val = f32_to_bf8(row + dq + i);
+      if (cached)
+        *reinterpret_cast<uint4*>(k_cache + ((page * kvh + kh) * page_size + off) * hd + d) = val;
+      if (k_dense) *reinterpret_cast<uint4*>(k_dense + (size_t)t * dk + i) = val;
+    }
+    const float m = earlier ? lam[0] : 0.f;
+    for (int c = tid; c < dv >> 3; c += PP_THREADS) {
+      const int i = 8 * c, kh = i / vd, d = i - kh * vd;
+      uint4 val = *reinterpret_cast<const uint4*>(src + dq + dk + i);
+      if (earlier) {
+        float v[8], e8[8];
+        bf8_to_f32(val, v);
+        bf8_to_f32(*reinterpret_cast<const uint4*>(earlier + (size_t)t * ld_earlier + i), e8);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = (1.0f - m) * v[e] + m * e8[e];
+        val = f32_to_bf8(v);
+      }
+      if (cached)
+        *reinterpret_cast<uint4*>(v_cache + ((page * kvh + kh) * page_size + off) * vd + d) = val;
+      if (v_dense) *reinterpret_cast<uint4*>(v_dense + (size_t)t * dv + i) = val;
+    }
+  } else {
+  for (int i = tid; i < dq; i += PP_THREADS) qo[i] = from_f32<TA>(row[i]);
   for (int i = tid; i < dk; i += PP_THREADS) {
     const int kh = i / hd, d = i - kh * hd;
     const TA val = from_f32<TA>(row[dq + i]);
@@ -164,6 +228,7 @@ attention_prepare_kernel(const TA* __restrict__ qkv, long long ld, const int* __
     const TA val = from_f32<TA>(v);
     if (cached) v_cache[((page * kvh + kh) * page_size + off) * vd + d] = val;
     if (v_dense) v_dense[(size_t)t * dv + i] = val;
+  }
   }
 }
 
@@ -184,20 +249,30 @@ IX_API int ix_attention_prepare(const void* qkv, long long ld, int dtype, const 
   if ((q_gain == nullptr) != (k_gain == nullptr) || (rot > 0 && !freq) || (earlier && !lam) ||
       (k_cache && (!v_cache || !slots)))
     return IX_ERR_SIZE;
-  const size_t smem = (size_t)(heads + kvh) * hd * sizeof(float);
+  const size_t smem = ((size_t)(heads + kvh) * hd + rot) * sizeof(float);
   if (smem > 200 * 1024) return IX_ERR_SMEM;
-  IX_DISPATCH_DTYPE(dtype, TA, {
-    auto kern = attention_prepare_kernel<TA>;
-    if (smem > 48 * 1024) {
-      cudaError_t e =
-          cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      if (e != cudaSuccess) return (int)e;
-    }
-    ix_launch(kern, dim3(T), dim3(PP_THREADS), smem, stream, (const TA*)qkv, ld, positions, freq,
-              magnitude, rot, interleaved, heads, kvh, hd, vd, q_gain, k_gain, eps, head_unit,
-              (const TA*)earlier, ld_earlier, lam, slots, (TA*)q_out, (TA*)k_cache, (TA*)v_cache,
-              page_size, (TA*)k_dense, (TA*)v_dense);
-  });
+  const bool vec =
+      dtype == IX_BF16 && hd % 8 == 0 && vd % 8 == 0 && ld % 8 == 0 && ld_earlier % 8 == 0 &&
+      (((uintptr_t)qkv | (uintptr_t)earlier | (uintptr_t)q_out | (uintptr_t)k_cache |
+        (uintptr_t)v_cache | (uintptr_t)k_dense | (uintptr_t)v_dense) & 15) == 0;
+#define PP_PREPARE(TA, VEC)                                                                     \
+  do {                                                                                          \
+    auto kern = attention_prepare_kernel<TA, VEC>;                                              \
+    if (smem > 48 * 1024) {                                                                     \
+      cudaError_t e =                                                                           \
+          cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
+      if (e != cudaSuccess) return (int)e;                                                      \
+    }                                                                                           \
+    ix_launch(kern, dim3(T), dim3(PP_THREADS), smem, stream, (const TA*)qkv, ld, positions,     \
+              freq, magnitude, rot, interleaved, heads, kvh, hd, vd, q_gain, k_gain, eps,       \
+              head_unit, (const TA*)earlier, ld_earlier, lam, slots, (TA*)q_out, (TA*)k_cache,  \
+              (TA*)v_cache, page_size, (TA*)k_dense, (TA*)v_dense);                             \
+  } while (0)
+  if (vec) PP_PREPARE(bf16, true);
+  else if (dtype == IX_BF16) PP_PREPARE(bf16, false);
+  else if (dtype == IX_F32) PP_PREPARE(float, false);
+  else return IX_ERR_DTYPE;
+#undef PP_PREPARE
   return ix_launch_status();
 }
 

@@ -581,6 +581,11 @@ def prepared(args):
             q, kp, vp, bt, step.cu_q, step.q_pos0, win, scale, 0.0, 4, True),
         "tiled fp32 weights": lambda i: ops.paged_attention_tiled(
             q, kp, vp, bt, step.cu_q, step.q_pos0, win, scale),
+        "mma.sync 16-bit weights, kept first keys, sink": lambda i:
+            ops.paged_attention_prefill_exact(q, kp, vp, bt, step.cu_q, step.q_pos0, win, scale,
+                                              4, True),
+        "mma.sync 8-bit weights (like, older form)": lambda i: ops.paged_attention_prefill(
+            q, kp, vp, bt, step.cu_q, step.q_pos0, win, scale, kernel="mma"),
         "tcgen05 (like)": lambda i: ops.paged_attention_prefill(
             q, kp, vp, bt, step.cu_q, step.q_pos0, win, scale, max_kv_len=T),
     }
@@ -602,6 +607,11 @@ def prepared(args):
             qd, kcs[i], vcs[i], btd, kv_len, C, win, scale, keep_first=4, sink=True),
         "any-size fp32 weights": lambda i: ops.paged_attention_decode_any(
             qd, kcs[i], vcs[i], btd, kv_len, C, win, scale),
+        "mma.sync 16-bit weights, kept first keys, sink": lambda i:
+            ops.paged_attention_decode_exact(qd, kcs[i], vcs[i], btd, kv_len, C, win, scale,
+                                             keep_first=4, sink=True),
+        "mma.sync 8-bit weights (like, older form)": lambda i: ops.paged_attention_decode(
+            qd, kcs[i], vcs[i], btd, kv_len, C, win, scale, kernel="mma"),
         "TMA (like)": lambda i: ops.paged_attention_decode(qd, kcs[i], vcs[i], btd, kv_len, C,
                                                            win, scale),
     }

@@ -812,6 +812,81 @@ def paged_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
     return out
 
 
+def paged_attention_prefill_exact(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                                  block_table: torch.Tensor, cu_q: torch.Tensor,
+                                  q_pos0: torch.Tensor, window: int, scale: float,
+                                  keep_first: int = 0, sink: bool = False):
+    """Tensor-core attention (mma.sync) for a ragged batch of bfloat16 queries whose softmax
+    weights keep 16 bits in their product with the values (each weight enters as two
+    bfloat16 terms into the same fp32 accumulator): for decoders that want scores and
+    weights in 32-bit arithmetic.  Key and value heads of 64 or 128 entries each (they may
+    differ); ``keep_first`` and ``sink`` as in ``paged_attention``."""
+    _chk("q", q, torch.bfloat16)
+    _chk("k_cache", k_cache, q.dtype)
+    _chk("v_cache", v_cache, q.dtype)
+    _chk("block_table", block_table, torch.int32)
+    _chk("cu_q", cu_q, torch.int32)
+    _chk("q_pos0", q_pos0, torch.int32)
+    T, heads, hd = q.shape
+    P, kvh, page, chd = k_cache.shape
+    vd = v_cache.shape[3]
+    S = q_pos0.numel()
+    if chd != hd or tuple(v_cache.shape[:3]) != (P, kvh, page):
+        raise KernelError("paged_attention_prefill_exact: cache geometry differs from the "
+                          "query's")
+    if cu_q.numel() != S + 1 or block_table.shape[0] != S:
+        raise KernelError("paged_attention_prefill_exact: cu_q, q_pos0 and block_table disagree")
+    out = torch.empty((T, heads, vd), dtype=q.dtype, device=q.device)
+    _check(_lib().ix_paged_attention_prefill_exact(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(cu_q), _ptr(q_pos0),
+        _ptr(out), T, S, heads, kvh, hd, vd, page, block_table.shape[1], window,
+        ctypes.c_float(scale), int(keep_first), 1 if sink else 0, _stream()),
+        "paged_attention_prefill_exact")
+    _count()
+    return out
+
+
+def paged_attention_decode_exact(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                                 block_table: torch.Tensor, kv_len: torch.Tensor, max_kv_len: int,
+                                 window: int, scale: float, splits: Optional[int] = None,
+                                 keep_first: int = 0, sink: bool = False):
+    """Split-KV tensor-core attention (mma.sync) for a batch in which sequence s brings the
+    one bfloat16 query q[s] at position kv_len[s] - 1, with softmax weights that keep 16 bits
+    in their product with the values; key and value heads of 64 or 128 entries each."""
+    _chk("q", q, torch.bfloat16)
+    _chk("k_cache", k_cache, q.dtype)
+    _chk("v_cache", v_cache, q.dtype)
+    _chk("block_table", block_table, torch.int32)
+    _chk("kv_len", kv_len, torch.int32)
+    S, heads, hd = q.shape
+    P, kvh, page, chd = k_cache.shape
+    vd = v_cache.shape[3]
+    if chd != hd or tuple(v_cache.shape[:3]) != (P, kvh, page):
+        raise KernelError("paged_attention_decode_exact: cache geometry differs from the query's")
+    if kv_len.numel() != S or block_table.shape[0] != S:
+        raise KernelError("paged_attention_decode_exact: one query per sequence is required")
+    lib = _lib()
+    if splits is None:
+        span = min(int(max_kv_len), window + keep_first) if window > 0 else int(max_kv_len)
+        splits = lib.ix_attn_decode_splits(S, heads, kvh, span)
+    out = torch.empty((S, heads, vd), dtype=q.dtype, device=q.device)
+    part_o = part_ml = None
+    if splits > 1:
+        part_o = torch.empty((S, heads, splits, vd), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((S, heads, splits, 2), dtype=torch.float32, device=q.device)
+    _check(lib.ix_paged_attention_decode_exact(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(kv_len), _ptr(part_o),
+        _ptr(part_ml), _ptr(out), S, heads, kvh, hd, vd, page, block_table.shape[1], window,
+        ctypes.c_float(scale), splits, int(keep_first), 1 if sink else 0, _stream()),
+        "paged_attention_decode_exact")
+    _count(2 if splits > 1 else 1)
+    return out
+
+
+# The fp32-weights path takes the tensor-core kernels with 16-bit weights where they apply.
+USE_EXACT_TC_ATTENTION = True
+
+
 def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                     block_table: torch.Tensor, step, window: int, scale: float,
                     softcap: float = 0.0, fp32_weights: bool = False, keep_first: int = 0,
@@ -904,12 +979,36 @@ def _paged_attention_softcap(q, k_cache, v_cache, block_table, step, window, sca
                              keep_first=0, sink=False):
     """The fp32-arithmetic kernels (squashed scores or not)."""
     hd = q.shape[2]
+    if (USE_EXACT_TC_ATTENTION and softcap == 0.0 and scale > 0 and q.dtype == torch.bfloat16
+            and getattr(step, "all_decode", False) and getattr(step, "kv_len", None) is not None
+            and step.num_tokens == step.num_seqs
+            and _lib().ix_paged_attention_decode_exact_applies(hd, v_cache.shape[3])):
+        return paged_attention_decode_exact(q, k_cache, v_cache, block_table, step.kv_len,
+                                            step.max_kv_len, window, scale,
+                                            keep_first=keep_first, sink=sink)
     if (getattr(step, "all_decode", False) and getattr(step, "kv_len", None) is not None
             and step.num_tokens == step.num_seqs and step.max_kv_len >= DECODE_ANY_MIN_KEYS
             and max(hd, v_cache.shape[3]) <= 512):
         return paged_attention_decode_any(q, k_cache, v_cache, block_table, step.kv_len,
                                           step.max_kv_len, window, scale, softcap,
                                           keep_first=keep_first, sink=sink)
+    if (USE_EXACT_TC_ATTENTION and softcap == 0.0 and scale > 0 and q.dtype == torch.bfloat16
+            and _lib().ix_paged_attention_prefill_exact_applies(hd, v_cache.shape[3])
+            and getattr(step, "cu_q", None) is not None):
+        nd = getattr(step, "num_decode_seqs", 0)
+        if (0 < nd < step.num_seqs and getattr(step, "cu_q_prompt", None) is not None
+                and getattr(step, "kv_len", None) is not None):
+            # a mixed batch: its single tokens (they come first) go to the split-KV kernel,
+            # the prompt portions to the tiled one
+            single = paged_attention_decode_exact(
+                q[:nd], k_cache, v_cache, block_table[:nd], step.kv_len[:nd], step.max_kv_len,
+                window, scale, keep_first=keep_first, sink=sink)
+            rest = paged_attention_prefill_exact(
+                q[nd:], k_cache, v_cache, block_table[nd:], step.cu_q_prompt, step.q_pos0[nd:],
+                window, scale, keep_first, sink)
+            return torch.cat([single, rest], dim=0)
+        return paged_attention_prefill_exact(q, k_cache, v_cache, block_table, step.cu_q,
+                                             step.q_pos0, window, scale, keep_first, sink)
     if (step.num_tokens >= TILED_ATTENTION_MIN_QUERIES * step.num_seqs
             and _lib().ix_paged_attention_tiled_applies(hd)
             and _lib().ix_paged_attention_tiled_applies(v_cache.shape[3])

@@ -117,12 +117,18 @@ def test_preparation_of_q_k_v(dtype, heads, kvh, hd, vd, rot, inter, proj, unit)
     """Projection norm, rotation in both pairings with a factor on cos and sin, unit heads,
     value blend, the dense q and the page writes, on rows that are views of a wider one."""
     g = torch.Generator().manual_seed(heads * hd + rot)
+    # views that start off a 16-byte mark, and on one (the kernel's two forms)
+    for lead, lead_e in ((3, 4), (8, 16)):
+        _prepare_case(dtype, heads, kvh, hd, vd, rot, inter, proj, unit, g, lead, lead_e)
+
+
+def _prepare_case(dtype, heads, kvh, hd, vd, rot, inter, proj, unit, g, lead, lead_e):
     T, page, pages = 11, 4, 9
     dq, dk, dv = heads * hd, kvh * hd, kvh * vd
-    wide = (torch.randn(T, dq + dk + dv + 5, generator=g) * 2.0).to(dtype)
-    qkv = wide[:, 3:3 + dq + dk + dv]
-    earlier_wide = torch.randn(T, dv + 9, generator=g).to(dtype)
-    earlier = earlier_wide[:, 4:4 + dv]
+    wide = (torch.randn(T, dq + dk + dv + 16, generator=g) * 2.0).to(dtype)
+    qkv = wide[:, lead:lead + dq + dk + dv]
+    earlier_wide = torch.randn(T, dv + 24, generator=g).to(dtype)
+    earlier = earlier_wide[:, lead_e:lead_e + dv]
     pos = torch.tensor([0, 1, 2, 3, 900, 901, 7, 8, 9, 65, 66], dtype=torch.int32)
     freq = (torch.rand(rot // 2, generator=g) * 1.5) if rot else None
     qg = (1.0 + 0.3 * torch.randn(dq, generator=g)) if proj else None
@@ -140,8 +146,9 @@ def test_preparation_of_q_k_v(dtype, heads, kvh, hd, vd, rot, inter, proj, unit)
         wide_d = wide.cuda()
         early_d = earlier_wide.cuda()
         q, k, v = _ops().attention_prepare(
-            wide_d[:, 3:3 + dq + dk + dv], pos.cuda(), dev(freq), 1.07, rot, inter, heads, kvh,
-            hd, vd, dev(qg), dev(kg), 1e-5, unit, None if mix is None else early_d[:, 4:4 + dv],
+            wide_d[:, lead:lead + dq + dk + dv], pos.cuda(), dev(freq), 1.07, rot, inter, heads,
+            kvh, hd, vd, dev(qg), dev(kg), 1e-5, unit,
+            None if mix is None else early_d[:, lead_e:lead_e + dv],
             lam.cuda(), kc, vc, slots.cuda(), want_dense_kv=True)
         for got, want in ((q, q_ref), (k, k_ref), (v, v_ref), (kc, kc_ref), (vc, vc_ref)):
             torch.testing.assert_close(got.cpu().float(), want.float(), **_tol(dtype))
@@ -300,6 +307,49 @@ def test_single_token_attention_in_splits_with_kept_keys_and_sink(dtype, H, G, D
         torch.testing.assert_close(til, ref, **_tol(dtype))
 
 
+@pytest.mark.parametrize("H,G,D,VD", [(8, 2, 64, 64), (4, 4, 64, 128), (16, 2, 128, 64),
+                                      (20, 1, 128, 128)])
+@pytest.mark.parametrize("window,keep,sink", [(0, 0, False), (100, 4, False), (100, 0, True),
+                                              (70, 130, True), (1, 1, False)])
+def test_tensor_core_attention_with_16_bit_weights(H, G, D, VD, window, keep, sink):
+    """The mma.sync kernels whose weights enter the product with the values as two bfloat16
+    terms: prompts of unequal length beside each other and single tokens in splits, against
+    the statement with 32-bit weights, and far closer to the CUDA-core kernel with 32-bit
+    weights than one rounding of a weight to bfloat16 would leave them."""
+    dtype, page, scale = torch.bfloat16, 16, 0.35
+    k = keep if window else 0
+    q_lens, starts = [70, 5, 130, 1], [200, 0, 63, 400]
+    step, bt, kc, vc, q = _kv_case(H + VD, H, G, D, VD, page, q_lens, starts, dtype)
+    vc = vc + 3.0          # values with a mean: an error of the weights does not average out
+    ref = host_ops.paged_attention_generic(q, kc, vc, bt, step.seq_of_token, step.positions,
+                                           window, scale, 0.0, k, sink).float()
+    cs = _cuda(step)
+    out = _ops().paged_attention_prefill_exact(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), cs.cu_q,
+                                               cs.q_pos0, window, scale, k, sink).cpu().float()
+    torch.testing.assert_close(out, ref, **_tol(dtype))
+    exact = _ops().paged_attention_tiled(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), cs.cu_q,
+                                         cs.q_pos0, window, scale, 0.0, k, sink).cpu().float()
+    # both round their result to bfloat16 once: they differ by that rounding at most
+    assert float((out - exact).abs().max()) <= 2.0 ** -7 * float(exact.abs().max())
+    assert float((out - exact).abs().mean()) <= 2.0 ** -11 * float(exact.abs().max())
+    q_lens, starts = [1, 1, 1, 1], [0, 129, 999, 63]
+    step, bt, kc, vc, q = _kv_case(H + D, H, G, D, VD, page, q_lens, starts, dtype)
+    vc = vc + 3.0
+    ref = host_ops.paged_attention_generic(q, kc, vc, bt, step.seq_of_token, step.positions,
+                                           window, scale, 0.0, k, sink).float()
+    cs = _cuda(step)
+    for splits in (None, 1, 7):
+        out = _ops().paged_attention_decode_exact(
+            q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), cs.kv_len, cs.max_kv_len, window, scale,
+            splits=splits, keep_first=k, sink=sink).cpu().float()
+        torch.testing.assert_close(out, ref, **_tol(dtype))
+        assert float((out - ref).abs().mean()) <= 2.0 ** -10 * float(ref.abs().max())
+    # the dispatcher takes these kernels for such heads
+    via = _ops().paged_attention(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), cs, window, scale,
+                                 fp32_weights=True, keep_first=k, sink=sink).cpu().float()
+    torch.testing.assert_close(via, out)
+
+
 def test_prompt_attention_does_not_depend_on_the_cut():
     """A sequence's queries whole and in portions that start inside a tile, with kept keys
     and the sink: the tiled kernel gives the same bits."""
@@ -354,7 +404,7 @@ def test_long_decoding_with_recorded_steps(tmp_path, dtype):
     sess = ReplaySession(d, dtype, traces.peak_tokens(steps), page_size=4, use_graphs=True)
     rows = mc.run_trace(sess, steps)
     assert len(rows) == 270 and sess.executor.graph_replays >= 200
-    rows = fk.rows_to_compare(dtype, d, reqs, rows, share=0.1)
+    rows = fk.rows_to_compare(dtype, d, reqs, rows, share=0.05)
     mc.compare(rows, ref, fk.bound_for(dtype, d, reqs), f"long decode {dtype}")
 
 
@@ -371,7 +421,7 @@ def test_long_prompts(tmp_path, dtype, kind):
     sess = ReplaySession(d, dtype, traces.peak_tokens(steps), page_size=16, max_live=4)
     rows = mc.run_trace(sess, steps)
     sess.executor.poll_errors()
-    rows = fk.rows_to_compare(dtype, d, reqs, rows, share=0.1)
+    rows = fk.rows_to_compare(dtype, d, reqs, rows, share=0.05)
     mc.compare(rows, ref, fk.bound_for(dtype, d, reqs), f"long/{kind}/{dtype}")
 
 
