@@ -13,6 +13,10 @@
 //    rounding and the rounding of what that left over, both into the same fp32
 //    accumulator: 16 bits of the weight instead of 8 (scores are exact products of
 //    bfloat16 numbers summed in fp32; maxima, exponentials and sums are fp32);
+//    With at most 8 query heads a key/value head (FOLD) rows 8..15 of the 16-row tile are
+//    idle, and the second term of head r rides there: row r + 8 of P holds what rounding
+//    row r left over, one product serves both, and row r + 8 of O is added to row r at the
+//    end.  Otherwise the second term is a second product.
 //  * value heads of a size of their own (64 or 128, as the keys');
 //  * `keep_first`: the sequence's first keep_first keys stay visible beside the window;
 //    the walk goes over them and then over the window as one range that is split;
@@ -64,7 +68,7 @@ __device__ __forceinline__ unsigned dx_pack(float lo, float hi) {
   return *reinterpret_cast<unsigned*>(&v);
 }
 
-template <int HD, int VD>
+template <int HD, int VD, bool FOLD>
 __global__ void __launch_bounds__(DX_THREADS)
 attn_decode_exact_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc,
                          const bf16* __restrict__ vc, const int* __restrict__ block_table,
@@ -117,6 +121,22 @@ attn_decode_exact_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc
       const int kbase = k0 + it * DX_BN;
       unsigned char* kd = Ks + stage * K_TILE;
       unsigned char* vd = Vs + stage * V_TILE;
+      if (CH == CHV) {        // equal sizes: a row's place is worked out once for both
+        for (int idx = tid; idx < DX_BN * CH; idx += DX_THREADS) {
+          const int r = idx / CH, c = idx - r * CH;
+          const int kw = kbase + r;
+          const bool ok = kw < k1;
+          size_t off = 0;
+          if (ok) {
+            const int kp = kw < start ? kw - shift : kw;
+            const int pi = page_shift >= 0 ? (kp >> page_shift) : (kp / page_size);
+            const int po = page_shift >= 0 ? (kp & (page_size - 1)) : (kp % page_size);
+            off = (((size_t)bt[pi] * kvh + kh) * page_size + po) * HD + c * 8;
+          }
+          dx_cp16(kd + dx_swz<CH>(r, c), kc + off, ok);
+          dx_cp16(vd + dx_swz<CH>(r, c), vc + off, ok);
+        }
+      } else
       for (int idx = tid; idx < DX_BN * (CH + CHV); idx += DX_THREADS) {
         const bool is_v = idx >= DX_BN * CH;
         const int j = is_v ? idx - DX_BN * CH : idx;
@@ -196,10 +216,11 @@ attn_decode_exact_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc
         m_run[r] = m_new;
         l_run[r] *= corr[r];
       }
+      // (FOLD: rows 8..15 of O belong to rows 0..7 and are rescaled with them)
 #pragma unroll
       for (int j = 0; j < DT; ++j) {
         o[j][0] *= corr[0]; o[j][1] *= corr[0];
-        o[j][2] *= corr[1]; o[j][3] *= corr[1];
+        o[j][2] *= corr[FOLD ? 0 : 1]; o[j][3] *= corr[FOLD ? 0 : 1];
       }
       unsigned pf[4], pl[4];
 #pragma unroll
@@ -213,9 +234,13 @@ attn_decode_exact_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc
         const __nv_bfloat162 ha = __floats2bfloat162_rn(p0, p1), hb = __floats2bfloat162_rn(p2, p3);
         const float2 fa = __bfloat1622float2(ha), fb = __bfloat1622float2(hb);
         pf[j * 2 + 0] = *reinterpret_cast<const unsigned*>(&ha);
-        pf[j * 2 + 1] = *reinterpret_cast<const unsigned*>(&hb);
-        pl[j * 2 + 0] = dx_pack(p0 - fa.x, p1 - fa.y);
-        pl[j * 2 + 1] = dx_pack(p2 - fb.x, p3 - fb.y);
+        if (FOLD) {
+          pf[j * 2 + 1] = dx_pack(p0 - fa.x, p1 - fa.y);      // row g + 8: the rest of row g
+        } else {
+          pf[j * 2 + 1] = *reinterpret_cast<const unsigned*>(&hb);
+          pl[j * 2 + 0] = dx_pack(p0 - fa.x, p1 - fa.y);
+          pl[j * 2 + 1] = dx_pack(p2 - fb.x, p3 - fb.y);
+        }
       }
 #pragma unroll
       for (int jd = 0; jd < DT; jd += 2) {
@@ -224,8 +249,10 @@ attn_decode_exact_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc
                                       jd + (lane >> 4)));
         dx_mma(o[jd], pf, b[0], b[1]);
         dx_mma(o[jd + 1], pf, b[2], b[3]);
-        dx_mma(o[jd], pl, b[0], b[1]);
-        dx_mma(o[jd + 1], pl, b[2], b[3]);
+        if (!FOLD) {
+          dx_mma(o[jd], pl, b[0], b[1]);
+          dx_mma(o[jd + 1], pl, b[2], b[3]);
+        }
       }
     }
     __syncthreads();   // the stage may be refilled
@@ -247,6 +274,10 @@ attn_decode_exact_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc
 #pragma unroll
   for (int j = 0; j < DT; ++j) {
     const int d = j * 8 + 2 * t;
+    if (FOLD) {            // the second terms' sums join the first terms'
+      o[j][0] += o[j][2];
+      o[j][1] += o[j][3];
+    }
     sm_o[(warp * 16 + g) * VD + d] = o[j][0];
     sm_o[(warp * 16 + g) * VD + d + 1] = o[j][1];
     sm_o[(warp * 16 + g + 8) * VD + d] = o[j][2];
@@ -326,12 +357,19 @@ static int launch_decode_exact(const void* q, const void* kc, const void* vc, co
   int page_shift = -1;
   if ((page_size & (page_size - 1)) == 0)
     for (page_shift = 0; (1 << page_shift) < page_size; ++page_shift) {}
-  auto kern = attn_decode_exact_kernel<HD, VD>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  if (e != cudaSuccess) return (int)e;
-  ix_launch(kern, grid, dim3(DX_THREADS), smem, stream, (const bf16*)q, (const bf16*)kc,
-            (const bf16*)vc, bt, kv_len, part_o, part_ml, (bf16*)out, heads, kvh, page_size,
-            page_shift, maxb, window, sl2, splits, keep_first, sink);
+#define DX_LAUNCH(FOLD_)                                                                        \
+  do {                                                                                          \
+    auto kern = attn_decode_exact_kernel<HD, VD, FOLD_>;                                        \
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
+                                         smem);                                                 \
+    if (e != cudaSuccess) return (int)e;                                                        \
+    ix_launch(kern, grid, dim3(DX_THREADS), smem, stream, (const bf16*)q, (const bf16*)kc,      \
+              (const bf16*)vc, bt, kv_len, part_o, part_ml, (bf16*)out, heads, kvh, page_size,  \
+              page_shift, maxb, window, sl2, splits, keep_first, sink);                         \
+  } while (0)
+  if (rep <= 8) DX_LAUNCH(true);
+  else DX_LAUNCH(false);
+#undef DX_LAUNCH
   int rc = ix_launch_status();
   if (rc != 0 || splits == 1) return rc;
   ix_launch(attn_decode_exact_merge_kernel, dim3(S * heads), dim3(VD >= 128 ? 128 : 64), 0,

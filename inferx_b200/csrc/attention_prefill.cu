@@ -346,6 +346,21 @@ attn_prefill_exact_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k
     const int kbase = tile_base(it);
     unsigned char* kd = Ks + stage * PF_BN * HD * 2;
     unsigned char* vd = Vs + stage * PF_BN * VD * 2;
+    if (CH == CHV) {          // equal sizes: a row's place is worked out once for both
+      for (int idx = tid; idx < PF_BN * CH; idx += PF_THREADS) {
+        const int r = idx / CH, c = idx - r * CH;
+        const int kp = kbase + r;
+        const bool ok = (kp >= kv_lo || kp < kept) && kp < kv_hi;
+        size_t off = 0;
+        if (ok) {
+          const int pi = page_shift >= 0 ? (kp >> page_shift) : (kp / page_size);
+          const int po = page_shift >= 0 ? (kp & (page_size - 1)) : (kp % page_size);
+          off = (((size_t)bt[pi] * kvh + kh) * page_size + po) * HD + c * 8;
+        }
+        cp_async16(kd + swz<CH>(r, c), kc + off, ok);
+        cp_async16(vd + swz<CH>(r, c), vc + off, ok);
+      }
+    } else
     for (int idx = tid; idx < PF_BN * (CH + CHV); idx += PF_THREADS) {
       const bool is_v = idx >= PF_BN * CH;
       const int j = is_v ? idx - PF_BN * CH : idx;
