@@ -258,9 +258,10 @@ class PreparedAttentionMixer:
         if s.projection_norm:
             decls += [TensorDecl(self._n("q_norm"), (self.dq,), keep="float32", init="gain"),
                       TensorDecl(self._n("k_norm"), (self.dk,), keep="float32", init="gain")]
-        if s.value_mix != "none":
-            # the layer that leaves its values has the scalar too; it is not used there
-            decls.append(TensorDecl(self._n("mix"), (), keep="float32", init="bias"))
+        # the layer that leaves its values has the scalar too (it is not used there); a layer
+        # that mixes nothing may have it in its checkpoint all the same
+        decls.append(TensorDecl(self._n("mix"), (), keep="float32", init="bias",
+                                optional=s.value_mix == "none"))
         return decls
 
     def bind(self, w):

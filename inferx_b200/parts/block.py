@@ -235,8 +235,12 @@ class DecoderModel:
         wl.check(self.tensors(), source, where)
         dt, dev = self.ctx.dtype, self.ctx.device
 
+        held = source.names()
+
         def fetch(decls):
-            return {d.name: wl.materialize(d, source, dt, dev) for d in decls}
+            # (a tensor declared optional is fetched only if the source has it)
+            return {d.name: wl.materialize(d, source, dt, dev) for d in decls
+                    if not getattr(d, "optional", False) or held is None or d.name in held}
 
         own = fetch(self._own_tensors())
         self.embed = own[self.spec.embed_name]

@@ -52,6 +52,9 @@ class TensorDecl:
     init: str = "matrix"   # "matrix" N(0,std) | "gain" 1+N(0,std) | "bias" N(0,std) | "zeros"
     # int32 tensors with init "distinct": every row holds distinct integers below ``high``
     high: int = 0
+    # a tensor the model does not use but a checkpoint of the design may hold: neither
+    # missing when it is absent nor unexpected when it is there
+    optional: bool = False
 
 
 class WeightSource:
@@ -239,7 +242,7 @@ def check(decls: Sequence[TensorDecl], source: WeightSource, where: str = "weigh
         return
     have = set(names)
     want = {d.name for d in decls}
-    missing = sorted(want - have)
+    missing = sorted({d.name for d in decls if not getattr(d, "optional", False)} - have)
     unexpected = sorted(have - want)
     wrong = []
     for d in decls:

@@ -319,3 +319,32 @@ def test_preemption_rebuilds_state_and_cache(tmp_path):
     roomy, p0 = run(64)
     tight, p1 = run(6)
     assert p0 == 0 and p1 >= 1 and roomy == tight
+
+
+def test_an_unused_blend_weight_may_be_there_or_not(tmp_path):
+    """A layer that mixes nothing has no use for the scalar; a folder runs with it and
+    without it, and a scalar that a mixing layer needs is still missed."""
+    import os
+    from inferx_b200.weights.loader import WeightError
+    from inferx_b200.weights.safetensors_io import Checkpoint, write_safetensors
+    d = fk.make_model_dir(fk.FA, tmp_path / "m", 3)
+    reqs = fk.make_requests(fk.FA, [9, 14], 1)
+    ref = fk.reference_rows(d, reqs)
+
+    def rewrite(drop):
+        ck = Checkpoint(d)
+        kept = {n: ck.get(n).clone() for n in ck.names() if n != drop}
+        ck.close()
+        write_safetensors(os.path.join(d, "model.safetensors"), kept.items(),
+                          metadata={"format": "pt"})
+
+    def replay():
+        sess = ReplaySession(d, "float32", 128, page_size=4, max_live=2, device="cpu",
+                             ops=host_ops)
+        return mc.run_trace(sess, traces.whole(reqs))
+    mc.compare(replay(), ref, 2e-5, "with the unused scalar")
+    rewrite("l3.mix.vmix")
+    mc.compare(replay(), ref, 2e-5, "without the unused scalar")
+    rewrite("l2.mix.vmix")
+    with pytest.raises(WeightError, match="l2.mix.vmix"):
+        replay()

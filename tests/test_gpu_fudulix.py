@@ -484,3 +484,38 @@ def test_greedy_generation_through_the_engine(tmp_path):
             assert tok == int(lg.argmax()) or float(top[0] - top[1]) < 1e-4 * float(lg.abs().max())
             seq.append(tok)
         assert len(c_out.output_tokens) == 12
+
+
+def test_command_line_and_sampling(tmp_path):
+    """The generation program takes a folder of the design like any other: greedy output is
+    the plain model's, and sampling with a seed (temperature, top-k, top-p, a repetition
+    penalty) gives the same tokens twice."""
+    d = fk.make_model_dir(fk.FB, tmp_path / "m", 9)
+    c, w = plain.read_model_folder(d)
+    base = [sys.executable, os.path.join(ROOT, "bin", "inferx-generate"), d, "--dtype", "fp32",
+            "--block-size", "4", "--max-model-len", "64", "--max-num-seqs", "2",
+            "--num-gpu-blocks-override", "48", "--log-level", "warning"]
+    p = subprocess.run(base + ["--prompt-ids", "5,17,3,90,41", "--prompt-ids", "9 8 7",
+                               "--max-tokens", "6", "--ignore-eos"],
+                       capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    lines = [json.loads(ln) for ln in p.stdout.splitlines() if ln.startswith("{")]
+    assert [l["index"] for l in lines] == [0, 1]
+    for line, prompt in zip(lines, ([5, 17, 3, 90, 41], [9, 8, 7])):
+        seq = list(prompt)
+        for tok in line["output_ids"]:
+            lg = plain.forward(c, w, seq)[-1]
+            top = torch.topk(lg, 2).values
+            assert tok == int(lg.argmax()) or float(top[0] - top[1]) < 1e-4 * float(lg.abs().max())
+            seq.append(tok)
+        assert len(line["output_ids"]) == 6
+    sampled = []
+    for _ in range(2):
+        p = subprocess.run(base + ["--prompt-ids", "9 8 7", "--max-tokens", "8", "--ignore-eos",
+                                   "--temperature", "0.9", "--top-k", "20", "--top-p", "0.9",
+                                   "--seed", "3", "--repetition-penalty", "1.2"],
+                           capture_output=True, text=True, timeout=600)
+        assert p.returncode == 0, p.stderr[-2000:]
+        (line,) = [json.loads(ln) for ln in p.stdout.splitlines() if ln.startswith("{")]
+        sampled.append(line["output_ids"])
+    assert sampled[0] == sampled[1] and len(sampled[0]) == 8
