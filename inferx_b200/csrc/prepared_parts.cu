@@ -81,12 +81,17 @@ IX_API int ix_embed_pair_norm(const void* table, const void* pairs, int dtype, c
 }
 
 // ---------------------------------------------------------------------------
+// Threads of a block of the preparation kernel: with 128 a multiprocessor holds sixteen
+// blocks, so that all tokens of a 2,048-token step are in flight at once and one block's
+// barriers are covered by the others' loads.
+#define PA_THREADS 128
+
 // One block per token.  The q and k parts of the row are held in shared memory as fp32
 // from the first read to the last write.  VEC (bfloat16 rows whose parts start on 16-byte
 // marks and whose head sizes are multiples of 8): the row is read and everything is written
 // in 16-byte accesses; the arithmetic and its order are the same.
 template <typename TA, bool VEC>
-__global__ void __launch_bounds__(PP_THREADS)
+__global__ void __launch_bounds__(PA_THREADS)
 attention_prepare_kernel(const TA* __restrict__ qkv, long long ld, const int* __restrict__ positions,
                          const float* __restrict__ freq, float magnitude, int rot, int interleaved,
                          int heads, int kvh, int hd, int vd, const float* __restrict__ q_gain,
@@ -106,7 +111,7 @@ attention_prepare_kernel(const TA* __restrict__ qkv, long long ld, const int* __
   float* turn = row + dq + dk;              // cos of pair i, then sin of pair i
   if (rot > 0) {                            // once per token: every head turns by the same angles
     const float pos = (float)positions[t];
-    for (int i = tid; i < (rot >> 1); i += PP_THREADS) {
+    for (int i = tid; i < (rot >> 1); i += PA_THREADS) {
       float sn, cs;
       sincosf(pos * freq[i], &sn, &cs);
       turn[i] = cs * magnitude;
@@ -116,7 +121,7 @@ attention_prepare_kernel(const TA* __restrict__ qkv, long long ld, const int* __
   float sq = 0.f, sk = 0.f;
   if constexpr (VEC) {
     const uint4* src8 = reinterpret_cast<const uint4*>(src);
-    for (int c = tid; c < (dq + dk) >> 3; c += PP_THREADS) {
+    for (int c = tid; c < (dq + dk) >> 3; c += PA_THREADS) {
       float x[8];
       bf8_to_f32(src8[c], x);
       float ss = 0.f;
@@ -128,7 +133,7 @@ attention_prepare_kernel(const TA* __restrict__ qkv, long long ld, const int* __
       if (8 * c < dq) sq += ss; else sk += ss;
     }
   } else {
-    for (int i = tid; i < dq + dk; i += PP_THREADS) {
+    for (int i = tid; i < dq + dk; i += PA_THREADS) {
       const float x = to_f32(src[i]);
       row[i] = x;
       if (i < dq) sq += x * x; else sk += x * x;
@@ -146,20 +151,20 @@ attention_prepare_kernel(const TA* __restrict__ qkv, long long ld, const int* __
       }
       __syncthreads();
       sq = sk = 0.f;
-      for (int w = 0; w < PP_THREADS / 32; ++w) {     // ascending warps: a fixed order
+      for (int w = 0; w < PA_THREADS / 32; ++w) {     // ascending warps: a fixed order
         sq += scratch[2 * w];
         sk += scratch[2 * w + 1];
       }
     }
     const float iq = 1.0f / sqrtf(sq / (float)dq + eps);
     const float ik = 1.0f / sqrtf(sk / (float)dk + eps);
-    for (int i = tid; i < dq + dk; i += PP_THREADS)
+    for (int i = tid; i < dq + dk; i += PA_THREADS)
       row[i] = i < dq ? row[i] * iq * q_gain[i] : row[i] * ik * k_gain[i - dq];
   }
   __syncthreads();
   if (rot > 0) {
     const int half = rot >> 1;
-    for (int idx = tid; idx < (heads + kvh) * half; idx += PP_THREADS) {
+    for (int idx = tid; idx < (heads + kvh) * half; idx += PA_THREADS) {
       const int h = idx / half, i = idx - h * half;
       const float cs = turn[i], sn = turn[half + i];
       float* v = row + (size_t)h * hd;
@@ -172,7 +177,7 @@ attention_prepare_kernel(const TA* __restrict__ qkv, long long ld, const int* __
   }
   if (head_unit) {
     const int lane = tid & 31, warp = tid >> 5;
-    for (int h = warp; h < heads + kvh; h += PP_THREADS / 32) {
+    for (int h = warp; h < heads + kvh; h += PA_THREADS / 32) {
       float* v = row + (size_t)h * hd;
       float ss = 0.f;
       for (int d = lane; d < hd; d += 32) ss += v[d] * v[d];
@@ -187,9 +192,9 @@ attention_prepare_kernel(const TA* __restrict__ qkv, long long ld, const int* __
   const bool cached = k_cache != nullptr && slot >= 0;
   const size_t page = cached ? slot / page_size : 0, off = cached ? slot % page_size : 0;
   if constexpr (VEC) {
-    for (int c = tid; c < dq >> 3; c += PP_THREADS)
+    for (int c = tid; c < dq >> 3; c += PA_THREADS)
       reinterpret_cast<uint4*>(qo)[c] = f32_to_bf8(row + 8 * c);
-    for (int c = tid; c < dk >> 3; c += PP_THREADS) {
+    for (int c = tid; c < dk >> 3; c += PA_THREADS) {
       const int i = 8 * c, kh = i / hd, d = i - kh * hd;
       const uint4 val = f32_to_bf8(row + dq + i);
       if (cached)
@@ -197,7 +202,7 @@ attention_prepare_kernel(const TA* __restrict__ qkv, long long ld, const int* __
       if (k_dense) *reinterpret_cast<uint4*>(k_dense + (size_t)t * dk + i) = val;
     }
     const float m = earlier ? lam[0] : 0.f;
-    for (int c = tid; c < dv >> 3; c += PP_THREADS) {
+    for (int c = tid; c < dv >> 3; c += PA_THREADS) {
       const int i = 8 * c, kh = i / vd, d = i - kh * vd;
       uint4 val = *reinterpret_cast<const uint4*>(src + dq + dk + i);
       if (earlier) {
@@ -213,15 +218,15 @@ attention_prepare_kernel(const TA* __restrict__ qkv, long long ld, const int* __
       if (v_dense) *reinterpret_cast<uint4*>(v_dense + (size_t)t * dv + i) = val;
     }
   } else {
-  for (int i = tid; i < dq; i += PP_THREADS) qo[i] = from_f32<TA>(row[i]);
-  for (int i = tid; i < dk; i += PP_THREADS) {
+  for (int i = tid; i < dq; i += PA_THREADS) qo[i] = from_f32<TA>(row[i]);
+  for (int i = tid; i < dk; i += PA_THREADS) {
     const int kh = i / hd, d = i - kh * hd;
     const TA val = from_f32<TA>(row[dq + i]);
     if (cached) k_cache[((page * kvh + kh) * page_size + off) * hd + d] = val;
     if (k_dense) k_dense[(size_t)t * dk + i] = val;
   }
   const float m = earlier ? lam[0] : 0.f;
-  for (int i = tid; i < dv; i += PP_THREADS) {
+  for (int i = tid; i < dv; i += PA_THREADS) {
     float v = to_f32(src[dq + dk + i]);
     if (earlier) v = (1.0f - m) * v + m * to_f32(earlier[(size_t)t * ld_earlier + i]);
     const int kh = i / vd, d = i - kh * vd;
@@ -263,7 +268,7 @@ IX_API int ix_attention_prepare(const void* qkv, long long ld, int dtype, const 
           cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
       if (e != cudaSuccess) return (int)e;                                                      \
     }                                                                                           \
-    ix_launch(kern, dim3(T), dim3(PP_THREADS), smem, stream, (const TA*)qkv, ld, positions,     \
+    ix_launch(kern, dim3(T), dim3(PA_THREADS), smem, stream, (const TA*)qkv, ld, positions,     \
               freq, magnitude, rot, interleaved, heads, kvh, hd, vd, q_gain, k_gain, eps,       \
               head_unit, (const TA*)earlier, ld_earlier, lam, slots, (TA*)q_out, (TA*)k_cache,  \
               (TA*)v_cache, page_size, (TA*)k_dense, (TA*)v_dense);                             \
