@@ -87,7 +87,14 @@ __device__ __forceinline__ float fa_max3(float a, float b, float c) {
   return m;
 }
 
-template <int HD>
+// EXACT: for decoders that want their softmax weights in 32-bit arithmetic.  A weight enters
+// its product with the values as two bfloat16 terms, its rounding and the rounding of what
+// that left over: the second term takes the 32 columns of the score buffer that the first
+// leaves free, and a second product adds it into the same accumulator (16 bits of the
+// weight).  The sequence's first `keep_first` keys stay visible beside the window (their
+// tiles are walked first) and `sink` adds one to the softmax's denominator.  One run of
+// keys per query tile (nsplit 1).
+template <int HD, bool EXACT>
 __global__ void __launch_bounds__(FA_THREADS, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                        const __grid_constant__ CUtensorMap map_k,
@@ -97,7 +104,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                        int kvh, int page_size, int page_shift, int maxb, int window,
                        float scale_log2e, int* __restrict__ status, int nsplit,
                        float* __restrict__ part_o, float* __restrict__ part_ml, float cap_c1,
-                       float cap_over_scale) {
+                       float cap_over_scale, int keep_first, int sink) {
   constexpr int HALVES = HD / 64;
   constexpr int Q_BYTES = FA_BM * HD * 2;
   constexpr int Q_HALF = FA_BM * 128;
@@ -147,7 +154,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
   const int n_all = (kv_hi - kt_first + FA_BN - 1) / FA_BN;
   const int per_split = (n_all + nsplit - 1) / nsplit;
   const int kt0 = kt_first + (int)blockIdx.z * per_split * FA_BN;
-  const int n_tiles = max(0, min(per_split, n_all - (int)blockIdx.z * per_split));
+  const int n_window = max(0, min(per_split, n_all - (int)blockIdx.z * per_split));
+  // keys below `kept` are visible although the window has passed them; their tiles (those
+  // that end before the window's first tile) come first in the walk
+  const int keep = EXACT ? keep_first : 0;
+  const int kept = (EXACT && window > 0) ? min(keep, kv_lo) : 0;
+  const int n_kept = EXACT ? min((kept + FA_BN - 1) / FA_BN, kt_first / FA_BN) : 0;
+  const int n_tiles = n_kept + n_window;
+  auto tile_key0 = [&](int j) { return j < n_kept ? j * FA_BN : kt0 + (j - n_kept) * FA_BN; };
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
   if ((smem_u32(smem) & 1023u) != 0) {           // the swizzle needs it; never seen
@@ -198,11 +212,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         tma_load_2d(Qs + hf * Q_HALF, &map_q, h * HD + hf * 64, tok0 + q0, &bars->q_full);
     }
     auto page_live = [&](int j) {
-      const int kp = kt0 + j * FA_BN + (lane << page_shift);
-      return lane < pages_per_tile && j < n_tiles && kp + page_size > kv_lo && kp < kv_hi;
+      const int kp = tile_key0(j) + (lane << page_shift);
+      if (!(lane < pages_per_tile && j < n_tiles)) return false;
+      // (a page of the window's first tile may lie wholly below the window and hold kept keys)
+      return j < n_kept ? kp < kept : ((kp + page_size > kv_lo || kp < kept) && kp < kv_hi);
     };
     auto page_id = [&](int j) {
-      return page_live(j) ? bt[((kt0 + j * FA_BN) >> page_shift) + lane] : -1;
+      return page_live(j) ? bt[(tile_key0(j) >> page_shift) + lane] : -1;
     };
     int pid_next = page_id(0);
     bool ok = true;
@@ -278,6 +294,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
           tc_mma_ts(tmem_base, tmem_base + S_COL + st * FA_BN + 8 * k4, vd, IDESC_PV,
                     (j > 0 || k4 > 0) ? 1u : 0u);
         }
+        if (EXACT) {      // the weights' second terms, from the other half of the buffer
+#pragma unroll
+          for (int k4 = 0; k4 < FA_BN / 16; ++k4) {
+            const unsigned long long vd =
+                umma_desc_mn(Vs + st * KV_TILE, KV_HALF, 1024) + 128 * k4;
+            tc_mma_ts(tmem_base, tmem_base + S_COL + st * FA_BN + 32 + 8 * k4, vd, IDESC_PV, 1u);
+          }
+        }
         tc_commit(&bars->v_empty[st]);
         tc_commit(&bars->o_done);
       }
@@ -304,14 +328,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
 #pragma unroll
         for (int i = 0; i < FA_BN; ++i) sc[i] = ix_cap_raw_score(sc[i], cap_c1, cap_over_scale);
       }
-      const int kbase = kt0 + j * FA_BN;
+      const int kbase = tile_key0(j);
       const bool need_mask = (kbase + FA_BN - 1 > pos0) || kbase < kv_lo ||
-                             (window > 0 && kbase < pmax - window + 1);
+                             (window > 0 && kbase < pmax - window + 1) || j < n_kept;
       if (need_mask) {
 #pragma unroll
         for (int i = 0; i < FA_BN; ++i) {
           const int kp = kbase + i;
-          if (kp > pos || kp < lo_r) sc[i] = -INFINITY;
+          if (kp > pos || (kp < lo_r && kp >= keep)) sc[i] = -INFINITY;
         }
       }
       // of the raw scores (the scale is positive); two chains, so that one max does not
@@ -336,6 +360,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       }
       const float nbase = m_ref == -INFINITY ? 0.f : -m_ref;
       float pk[FA_BN / 2];          // bf16 pairs, as the bit patterns tcgen05.st takes
+      float pl[EXACT ? FA_BN / 2 : 1];     // what the rounding of each pair left over
       float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
 #pragma unroll
       for (int i = 0; i < FA_BN; i += 4) {
@@ -348,6 +373,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1), v2 = __floats2bfloat162_rn(p2, p3);
         pk[i >> 1] = __uint_as_float(*reinterpret_cast<unsigned*>(&v));
         pk[(i >> 1) + 1] = __uint_as_float(*reinterpret_cast<unsigned*>(&v2));
+        if (EXACT) {
+          const float2 f = __bfloat1622float2(v), f2 = __bfloat1622float2(v2);
+          __nv_bfloat162 r = __floats2bfloat162_rn(p0 - f.x, p1 - f.y);
+          __nv_bfloat162 r2 = __floats2bfloat162_rn(p2 - f2.x, p3 - f2.y);
+          pl[i >> 1] = __uint_as_float(*reinterpret_cast<unsigned*>(&r));
+          pl[(i >> 1) + 1] = __uint_as_float(*reinterpret_cast<unsigned*>(&r2));
+        }
       }
       const float sum = (sum0 + sum1) + (sum2 + sum3);
       l_run += sum;
@@ -370,6 +402,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         }
       }
       tc_st32(lane_addr + S_COL + st * FA_BN, pk);
+      if (EXACT) tc_st32(lane_addr + S_COL + st * FA_BN + 32, pl);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->p_ready);
@@ -404,7 +437,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
       }
     } else if (n_tiles > 0) {
       tc_fence_after();
-      const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+      float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+      if (EXACT && sink && l_run > 0.f) {   // one more term, 2^(0 - reference), in the denominator
+        const float top = fmaxf(m_ref, 0.f);
+        const float c = fa_exp2(m_ref - top);
+        inv = c / (l_run * c + fa_exp2(-top));
+      }
       bf16* dst = out + ((size_t)(tok0 + q0 + row) * heads + h) * HD;
 #pragma unroll
       for (int c0 = 0; c0 < HD; c0 += 32) {
@@ -466,12 +504,13 @@ __global__ void attn_prefill_tc_merge_kernel(const float* __restrict__ part_o,
   }
 }
 
-template <int HD>
+template <int HD, bool EXACT = false>
 static int launch_prefill_tc(const void* q, const void* kc, const void* vc, long long cache_rows,
                              const int* bt, const int* cu_q, const int* q_pos0, void* out, int T,
                              int S, int heads, int kvh, int page_size, int page_shift, int maxb,
                              int window, float scale, float softcap, int* status, int nsplit,
-                             float* part_o, float* part_ml, cudaStream_t stream) {
+                             float* part_o, float* part_ml, cudaStream_t stream,
+                             int keep_first = 0, int sink = 0) {
   CUtensorMap map_q, map_k, map_v;
   int rc = ix_tensor_map_bf16_2d(&map_q, q, T, (long long)heads * HD, 64, FA_BM);
   if (rc != IX_OK) return rc;
@@ -480,7 +519,7 @@ static int launch_prefill_tc(const void* q, const void* kc, const void* vc, long
   rc = ix_tensor_map_bf16_2d(&map_v, vc, cache_rows, HD, 64, page_size);
   if (rc != IX_OK) return rc;
   const int smem = FA_BM * HD * 2 + 4 * FA_BN * HD * 2 + (int)sizeof(FaBars);
-  auto kern = attn_prefill_tc_kernel<HD>;
+  auto kern = attn_prefill_tc_kernel<HD, EXACT>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return (int)e;
   const int tiles = (T + FA_BM - 1) / FA_BM + S;   // every sequence can add one partial tile
@@ -492,7 +531,7 @@ static int launch_prefill_tc(const void* q, const void* kc, const void* vc, long
                                            part_ml,
                                            softcap > 0.f ? 2.f * scale * 1.4426950408889634f / softcap
                                                          : 0.f,
-                                           softcap > 0.f ? softcap / scale : 0.f);
+                                           softcap > 0.f ? softcap / scale : 0.f, keep_first, sink);
   rc = ix_launch_status();
   if (rc != IX_OK || nsplit == 1) return rc;
   attn_prefill_tc_merge_kernel<<<T * heads, HD >= 128 ? 128 : 64, 0, stream>>>(
@@ -581,4 +620,38 @@ static int prefill_tc_checked(const void* q, const void* k_cache, const void* v_
   return launch_prefill_tc<64>(q, k_cache, v_cache, cache_rows, block_table, cu_q, q_pos0, out, T,
                                S, heads, kvh, page_size, page_shift, max_blocks, window, scale,
                                softcap, status, splits, part_o, part_ml, stream);
+}
+
+// The EXACT form: weights of 16 bits in their product with the values, the sequence's first
+// `keep_first` keys kept beside the window, `sink` for one more term in the denominator.
+IX_API int ix_paged_attention_prefill_tc_exact_applies(int hd, int vd, int page_size) {
+  return hd == vd && (hd == 64 || hd == 128) &&
+         (page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64);
+}
+
+IX_API int ix_paged_attention_prefill_tc_exact(
+    const void* q, const void* k_cache, const void* v_cache, int num_pages,
+    const int* block_table, const int* cu_q, const int* q_pos0, void* out, int T, int S,
+    int heads, int kvh, int hd, int page_size, int max_blocks, int window, float scale,
+    int keep_first, int sink, int* status, cudaStream_t stream) {
+  if (T <= 0 || S <= 0) return IX_OK;
+  if (heads <= 0 || kvh <= 0 || heads % kvh != 0 || max_blocks <= 0 || window < 0 ||
+      keep_first < 0 || num_pages <= 0 || status == nullptr || heads > 65535 || !(scale > 0.f))
+    return IX_ERR_SIZE;
+  if (!ix_paged_attention_prefill_tc_exact_applies(hd, hd, page_size)) return IX_ERR_UNSUPPORTED;
+  if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15)
+    return IX_ERR_ALIGN;
+  int page_shift = 0;
+  while ((1 << page_shift) < page_size) ++page_shift;
+  const long long cache_rows = (long long)num_pages * kvh * page_size;
+  if (cache_rows > 0x7fffffffLL) return IX_ERR_SIZE;
+  if (hd == 128)
+    return launch_prefill_tc<128, true>(q, k_cache, v_cache, cache_rows, block_table, cu_q,
+                                        q_pos0, out, T, S, heads, kvh, page_size, page_shift,
+                                        max_blocks, window, scale, 0.f, status, 1, nullptr,
+                                        nullptr, stream, keep_first, sink);
+  return launch_prefill_tc<64, true>(q, k_cache, v_cache, cache_rows, block_table, cu_q, q_pos0,
+                                     out, T, S, heads, kvh, page_size, page_shift, max_blocks,
+                                     window, scale, 0.f, status, 1, nullptr, nullptr, stream,
+                                     keep_first, sink);
 }

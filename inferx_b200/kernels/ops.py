@@ -815,12 +815,15 @@ def paged_attention_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: tor
 def paged_attention_prefill_exact(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                                   block_table: torch.Tensor, cu_q: torch.Tensor,
                                   q_pos0: torch.Tensor, window: int, scale: float,
-                                  keep_first: int = 0, sink: bool = False):
-    """Tensor-core attention (mma.sync) for a ragged batch of bfloat16 queries whose softmax
-    weights keep 16 bits in their product with the values (each weight enters as two
-    bfloat16 terms into the same fp32 accumulator): for decoders that want scores and
-    weights in 32-bit arithmetic.  Key and value heads of 64 or 128 entries each (they may
-    differ); ``keep_first`` and ``sink`` as in ``paged_attention``."""
+                                  keep_first: int = 0, sink: bool = False,
+                                  kernel: Optional[str] = None):
+    """Tensor-core attention for a ragged batch of bfloat16 queries whose softmax weights
+    keep 16 bits in their product with the values (each weight enters as two bfloat16 terms
+    into the same fp32 accumulator): for decoders that want scores and weights in 32-bit
+    arithmetic.  Key and value heads of 64 or 128 entries each; ``keep_first`` and ``sink``
+    as in ``paged_attention``.  ``kernel``: "tc" (tcgen05; keys and values of the same size,
+    pages of 8 to 64 keys), "mma" (mma.sync; the sizes may differ, any page size); None
+    takes the first that applies."""
     _chk("q", q, torch.bfloat16)
     _chk("k_cache", k_cache, q.dtype)
     _chk("v_cache", v_cache, q.dtype)
@@ -837,6 +840,20 @@ def paged_attention_prefill_exact(q: torch.Tensor, k_cache: torch.Tensor, v_cach
     if cu_q.numel() != S + 1 or block_table.shape[0] != S:
         raise KernelError("paged_attention_prefill_exact: cu_q, q_pos0 and block_table disagree")
     out = torch.empty((T, heads, vd), dtype=q.dtype, device=q.device)
+    tc_ok = bool(_lib().ix_paged_attention_prefill_tc_exact_applies(hd, vd, page))
+    if kernel is None:
+        kernel = "tc" if USE_TCGEN05_ATTENTION and tc_ok else "mma"
+    if kernel not in ("tc", "mma") or (kernel == "tc" and not tc_ok):
+        raise KernelError(f"paged_attention_prefill_exact: no kernel form {kernel!r} for heads of "
+                          f"{hd} / {vd} and pages of {page}")
+    if kernel == "tc":
+        _check(_lib().ix_paged_attention_prefill_tc_exact(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), P, _ptr(block_table), _ptr(cu_q),
+            _ptr(q_pos0), _ptr(out), T, S, heads, kvh, hd, page, block_table.shape[1], window,
+            ctypes.c_float(scale), int(keep_first), 1 if sink else 0,
+            _ptr(_tc_status(q.device)), _stream()), "paged_attention_prefill_tc_exact")
+        _count()
+        return out
     _check(_lib().ix_paged_attention_prefill_exact(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(cu_q), _ptr(q_pos0),
         _ptr(out), T, S, heads, kvh, hd, vd, page, block_table.shape[1], window,
