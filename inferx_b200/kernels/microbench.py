@@ -581,9 +581,12 @@ def prepared(args):
             q, kp, vp, bt, step.cu_q, step.q_pos0, win, scale, 0.0, 4, True),
         "tiled fp32 weights": lambda i: ops.paged_attention_tiled(
             q, kp, vp, bt, step.cu_q, step.q_pos0, win, scale),
+        "tcgen05 16-bit weights, kept first keys, sink": lambda i:
+            ops.paged_attention_prefill_exact(q, kp, vp, bt, step.cu_q, step.q_pos0, win, scale,
+                                              4, True, kernel="tc"),
         "mma.sync 16-bit weights, kept first keys, sink": lambda i:
             ops.paged_attention_prefill_exact(q, kp, vp, bt, step.cu_q, step.q_pos0, win, scale,
-                                              4, True),
+                                              4, True, kernel="mma"),
         "mma.sync 8-bit weights (like, older form)": lambda i: ops.paged_attention_prefill(
             q, kp, vp, bt, step.cu_q, step.q_pos0, win, scale, kernel="mma"),
         "tcgen05 (like)": lambda i: ops.paged_attention_prefill(

@@ -312,7 +312,7 @@ def test_single_token_attention_in_splits_with_kept_keys_and_sink(dtype, H, G, D
 @pytest.mark.parametrize("window,keep,sink", [(0, 0, False), (100, 4, False), (100, 0, True),
                                               (70, 130, True), (1, 1, False)])
 def test_tensor_core_attention_with_16_bit_weights(H, G, D, VD, window, keep, sink):
-    """The mma.sync kernels whose weights enter the product with the values as two bfloat16
+    """The tensor-core kernels whose weights enter the product with the values as two bfloat16
     terms: prompts of unequal length beside each other and single tokens in splits, against
     the statement with 32-bit weights, and far closer to the CUDA-core kernel with 32-bit
     weights than one rounding of a weight to bfloat16 would leave them."""
@@ -324,14 +324,17 @@ def test_tensor_core_attention_with_16_bit_weights(H, G, D, VD, window, keep, si
     ref = host_ops.paged_attention_generic(q, kc, vc, bt, step.seq_of_token, step.positions,
                                            window, scale, 0.0, k, sink).float()
     cs = _cuda(step)
-    out = _ops().paged_attention_prefill_exact(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), cs.cu_q,
-                                               cs.q_pos0, window, scale, k, sink).cpu().float()
-    torch.testing.assert_close(out, ref, **_tol(dtype))
     exact = _ops().paged_attention_tiled(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), cs.cu_q,
                                          cs.q_pos0, window, scale, 0.0, k, sink).cpu().float()
-    # both round their result to bfloat16 once: they differ by that rounding at most
-    assert float((out - exact).abs().max()) <= 2.0 ** -7 * float(exact.abs().max())
-    assert float((out - exact).abs().mean()) <= 2.0 ** -11 * float(exact.abs().max())
+    # the tcgen05 form (keys and values of one size) and the mma.sync form (any of the four)
+    for form in (("tc", "mma") if D == VD else ("mma",)):
+        out = _ops().paged_attention_prefill_exact(
+            q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), cs.cu_q, cs.q_pos0, window, scale, k, sink,
+            kernel=form).cpu().float()
+        torch.testing.assert_close(out, ref, **_tol(dtype))
+        # both round their result to bfloat16 once: they differ by that rounding at most
+        assert float((out - exact).abs().max()) <= 2.0 ** -7 * float(exact.abs().max()), form
+        assert float((out - exact).abs().mean()) <= 2.0 ** -11 * float(exact.abs().max()), form
     q_lens, starts = [1, 1, 1, 1], [0, 129, 999, 63]
     step, bt, kc, vc, q = _kv_case(H + D, H, G, D, VD, page, q_lens, starts, dtype)
     vc = vc + 3.0
